@@ -1,0 +1,124 @@
+/*
+ * yan_b200 -- C ABI of the B200 (sm_100a) FP8 fine-grained-scaled GEMM path.
+ *
+ * Conventions (the same as the reference's generated entry point
+ * `extern "C" void launch(<args>, int& __return_code)`, yan/jit/template.py:130-137, called by
+ * yan/jit/runtime.py:30-68 through ctypes):
+ *   - every tensor is a raw device pointer (`tensor.data_ptr()`), every stream a `cudaStream_t`
+ *     passed as void* (`stream.cuda_stream`), sizes are C `int` (template.py:12-49);
+ *   - the caller allocates every buffer including the output; nothing here allocates or frees
+ *     device memory or synchronises the device; work is enqueued on the given stream only;
+ *   - the last parameter receives 0 when the work was enqueued, otherwise a YAN_B200_* code;
+ *     nothing is thrown across the boundary (runtime.py:66-68, yan/jit_kernels/tuner.py:45-50).
+ *   `int* return_code` is ABI-identical to the reference's `int& __return_code`.
+ *
+ * Layouts:
+ *   lhs         e4m3 [M, K] row-major                      (yan/include/gemm/fp8_gemm.cuh:43,57)
+ *   lhs_scales  fp32, k-block-major: element (kb, row) at kb * M + row, kb = k / 128
+ *                                                           (fp8_gemm.cuh:59; yan/jit_kernels/gemm.py:25)
+ *   rhs         e4m3 [N, K] row-major ("NT")                (fp8_gemm.cuh:44,58)
+ *   rhs_scales  fp32 [ceil(N/128), K/128] row-major         (fp8_gemm.cuh:41,55,60-61)
+ *   out         bf16 [M, ldd] row-major, ldd >= N           (fp8_gemm.cuh:56,87)
+ *   K % 128 == 0, N % 16 == 0; lhs/rhs/out 16-byte aligned; ldd % 8 == 0.
+ */
+#ifndef YAN_B200_H_
+#define YAN_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define YAN_B200_ABI_VERSION 1
+
+enum {
+    YAN_B200_OK = 0,
+    YAN_B200_BAD_ARGUMENT = 1,
+    YAN_B200_SMEM_TOO_LARGE = 2,
+    YAN_B200_TENSOR_MAP_FAILED = 3,
+    YAN_B200_LAUNCH_FAILED = 4,
+    YAN_B200_COMM_FAILED = 5,
+    YAN_B200_DEVICE_TIMEOUT = 6,
+    YAN_B200_WORKSPACE_TOO_SMALL = 7
+};
+
+/* Library identification.  No reference counterpart (the reference identifies a build by the hash
+ * of its headers, yan/jit/compiler.py:32-53). */
+int yan_b200_abi_version(void);
+const char* yan_b200_return_code_string(int code);
+
+/*
+ * FP8 GEMM, D = A . B^T with per-128-K scale promotion.  Replaces the launch the reference's template
+ * describes: yan/jit_kernels/gemm.py:9-31 (`Gemm<...>::run(out, rhs_scales, nullptr, m, descs..., stream,
+ * num_sms, smem_size)`) and the kernel yan/include/gemm/fp8_gemm.cuh:32-197.
+ * block_n: 0 = choose, else 32, 64, 128 or 256.  num_sms: CTAs of the persistent grid (<= device SMs).
+ */
+void yan_b200_gemm_fp8_fp8_bf16_nt(const void* lhs, const void* lhs_scales, const void* rhs, const void* rhs_scales,
+                                   void* out, int m, int n, int k, int ldd, void* stream, int num_sms, int block_n,
+                                   int* return_code);
+
+/* Same GEMM with an fp32 output [M, ldd] (ldd % 4 == 0): the K-split path can then sum fp32 partials.
+ * Takes the place of the fp32 partial tiles comm/gemm_allreduce.cu:57-60 reduces across ranks. */
+void yan_b200_gemm_fp8_fp8_f32_nt(const void* lhs, const void* lhs_scales, const void* rhs, const void* rhs_scales,
+                                  void* out, int m, int n, int k, int ldd, void* stream, int num_sms, int block_n,
+                                  int* return_code);
+
+/*
+ * Grouped GEMMs the reference's scheduler declares (yan/include/gemm/scheduler.cuh:7-11,42-48;
+ * `grouped_layout` kernel argument, fp8_gemm.cuh:41).
+ * contiguous: lhs [M, K] whose rows are grouped in 128-row-aligned runs
+ *             (yan/jit_kernels/utils.py:46-55), m_indices[M] = group of each row (-1 = padding row),
+ *             rhs [G, N, K], rhs_scales [G, N/128, K/128], out [M, N].
+ * masked:     lhs [G, m_max, K], lhs_scales k-block-major over G*m_max rows, rhs [G, N, K],
+ *             out [G, m_max, N]; only the first masked_m[g] rows of group g are computed.
+ */
+void yan_b200_m_grouped_gemm_fp8_fp8_bf16_nt_contiguous(const void* lhs, const void* lhs_scales, const void* rhs,
+                                                        const void* rhs_scales, void* out, const int* m_indices, int m,
+                                                        int n, int k, int num_groups, void* stream, int num_sms,
+                                                        int block_n, int* return_code);
+void yan_b200_m_grouped_gemm_fp8_fp8_bf16_nt_masked(const void* lhs, const void* lhs_scales, const void* rhs,
+                                                    const void* rhs_scales, void* out, const int* masked_m, int m_max,
+                                                    int n, int k, int num_groups, void* stream, int num_sms,
+                                                    int block_n, int* return_code);
+
+/*
+ * Activation quantizer: bf16 [M, x_ld] -> e4m3 [M, K] + fp32 scales (k-block-major, leading dimension
+ * scales_ld >= M), 1 x 128 groups, scale = amax/448.  The reference names this component but holds no
+ * code for it; the output feeds `lhs` / `lhs_scales` of the GEMM (yan/jit_kernels/gemm.py:23-25).
+ */
+void yan_b200_per_token_cast_to_fp8(const void* x, void* out, void* out_scales, int m, int k, int x_ld, int scales_ld,
+                                    void* stream, int* return_code);
+
+/* Weight quantizer: bf16 [N, K] -> e4m3 [N, K] + fp32 scales [N/128, K/128] (128 x 128 blocks); produces
+ * `rhs` / `rhs_scales` (fp8_gemm.cuh:41,44). */
+void yan_b200_per_block_cast_to_fp8(const void* w, void* out, void* out_scales, int n, int k, void* stream,
+                                    int* return_code);
+
+/*
+ * Quantize-then-GEMM in one call: out = bf16( quant_1x128(a) . rhs^T ).  `workspace` is caller-owned
+ * scratch of at least yan_b200_fp8_linear_workspace_bytes(m, k) bytes (256-byte aligned) that holds the
+ * quantized activations and their scales between the two kernels.  This is the path the north-star
+ * names end to end (bf16 A in, bf16 D out); the reference has no such function.
+ */
+size_t yan_b200_fp8_linear_workspace_bytes(int m, int k);
+void yan_b200_fp8_linear_bf16(const void* a, const void* rhs, const void* rhs_scales, void* out, void* workspace,
+                              size_t workspace_bytes, int m, int n, int k, int ldd, void* stream, int num_sms,
+                              int block_n, int* return_code);
+
+/*
+ * Device status word of the current device: 0, or (YAN_B200_DEVICE_TIMEOUT << 8) | site when a bounded
+ * device-side wait of the GEMM ran out.  Synchronises the device.  reset != 0 clears the word.
+ * Plays the role of the reference's error conventions (yan/jit/template.py:134 return code;
+ * comm/helper.h:26-53 CUDA_CHECK) for failures that only the device can see.
+ */
+void yan_b200_read_device_status(int* status, int reset, int* return_code);
+
+/* Sets the bound (nanoseconds, default 2e9) of every device-side wait of later GEMM launches. */
+void yan_b200_set_wait_timeout_ns(unsigned long long timeout_ns);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* YAN_B200_H_ */

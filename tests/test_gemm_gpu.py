@@ -1,0 +1,136 @@
+"""GPU parity of the FP8 GEMM against the CPU oracle (dequantize -> fp32 matmul -> bf16).
+
+Tolerance (both sides rounded to bf16): relative Frobenius error <= 1e-3 and max-abs error <= one bf16
+ulp at the binade of max|D_oracle|.
+"""
+import pytest
+import torch
+
+from oracle import ref
+
+pytestmark = pytest.mark.gpu
+
+REL_FRO_TOL = 1e-3
+
+
+def _operands(m, n, k, seed=0, outliers=False):
+    a, b = ref.make_inputs(m, n, k, seed=seed, outliers=outliers)
+    lhs = ref.per_token_cast_to_fp8(a)
+    rhs = ref.per_block_cast_to_fp8(b)
+    return lhs, rhs
+
+
+def _check(d, d_ref, what=""):
+    fro = ref.rel_frobenius(d, d_ref)
+    mx = ref.max_abs_err(d, d_ref)
+    bound = ref.bf16_ulp_at(float(d_ref.float().abs().max()))
+    assert fro <= REL_FRO_TOL, f"{what}: rel Frobenius {fro:.3e} > {REL_FRO_TOL}"
+    assert mx <= bound, f"{what}: max abs err {mx} > 1 bf16 ulp at max|D| ({bound})"
+
+
+def _run(lhs, rhs, block_n=0, out=None):
+    import yan_b200
+    m, n = lhs[0].shape[0], rhs[0].shape[0]
+    lhs_d = (lhs[0].cuda(), lhs[1].t().contiguous().cuda().t())
+    rhs_d = (rhs[0].cuda(), rhs[1].cuda())
+    if out is None:
+        out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    yan_b200.gemm_fp8_fp8_bf16_nt(lhs_d, rhs_d, out, block_n=block_n)
+    torch.cuda.synchronize()
+    assert yan_b200.read_device_status() == 0
+    return out
+
+
+@pytest.mark.parametrize("block_n", [0, 32, 64, 128, 256])
+def test_config1_all_tiles(cuda_lib, block_n):
+    """M=256 N=1024 K=1024 seed 0: the CPU-runnable configuration."""
+    lhs, rhs = _operands(256, 1024, 1024)
+    d = _run(lhs, rhs, block_n)
+    _check(d.cpu(), ref.ref_gemm(lhs, rhs), f"C1 block_n={block_n}")
+
+
+@pytest.mark.parametrize("m", [1, 7, 16, 64, 128, 129, 300])
+@pytest.mark.parametrize("n,k", [(128, 128), (256, 256), (384, 1024)])
+def test_small_shapes(cuda_lib, m, n, k):
+    lhs, rhs = _operands(m, n, k, seed=m + n + k)
+    d_ref = ref.ref_gemm(lhs, rhs)
+    for block_n in (0, 256):
+        d = _run(lhs, rhs, block_n)
+        _check(d.cpu(), d_ref, f"m={m} n={n} k={k} block_n={block_n}")
+
+
+@pytest.mark.parametrize("m", [16, 64])
+def test_decode_shape(cuda_lib, m):
+    """M in {16, 64}, N=7168, K=2048 with 1 % outlier channels x20."""
+    lhs, rhs = _operands(m, 7168, 2048, outliers=True)
+    d = _run(lhs, rhs)
+    _check(d.cpu(), ref.ref_gemm(lhs, rhs), f"decode m={m}")
+
+
+def test_long_k_many_tiles(cuda_lib):
+    """More tiles than SMs and a long K loop: exercises ring wrap-around and persistent scheduling."""
+    lhs, rhs = _operands(1024, 2560, 4096, seed=3)
+    d_ref = ref.ref_gemm(lhs, rhs)
+    for block_n in (128, 256):
+        _check(_run(lhs, rhs, block_n).cpu(), d_ref, f"block_n={block_n}")
+
+
+def test_output_slice_of_wider_buffer(cuda_lib):
+    """The N-split form writes a column slice of a full [M, N_total] buffer and must not touch the rest."""
+    lhs, rhs = _operands(192, 256, 512, seed=9)
+    full = torch.full((192, 1024), 7.0, dtype=torch.bfloat16, device="cuda")
+    _run(lhs, rhs, out=full[:, 512:768])
+    full = full.cpu()
+    _check(full[:, 512:768], ref.ref_gemm(lhs, rhs), "slice")
+    assert bool((full[:, :512] == 7.0).all()) and bool((full[:, 768:] == 7.0).all())
+
+
+def test_rows_beyond_m_are_not_written(cuda_lib):
+    lhs, rhs = _operands(130, 256, 256, seed=11)
+    buf = torch.full((256, 256), 3.0, dtype=torch.bfloat16, device="cuda")
+    _run(lhs, rhs, out=buf[:130])
+    assert bool((buf[130:].cpu() == 3.0).all())
+
+
+def test_linearity_in_scales(cuda_lib):
+    """Size-independent property: doubling every A scale doubles D exactly (power-of-two factor)."""
+    lhs, rhs = _operands(256, 512, 1024, seed=21)
+    d1 = _run(lhs, rhs).cpu().float()
+    d2 = _run((lhs[0], lhs[1] * 2.0), rhs).cpu().float()
+    assert torch.equal(d2, d1 * 2.0)
+
+
+def test_fp32_output(cuda_lib):
+    import yan_b200
+    lhs, rhs = _operands(200, 384, 1024, seed=4)
+    out = torch.empty(200, 384, dtype=torch.float32, device="cuda")
+    yan_b200.gemm_fp8_fp8_f32_nt((lhs[0].cuda(), lhs[1].t().contiguous().cuda().t()), (rhs[0].cuda(), rhs[1].cuda()), out)
+    d_ref = ref.ref_gemm_f32(lhs, rhs)
+    assert ref.rel_frobenius(out.cpu(), d_ref) <= 1e-5
+
+
+def test_fp8_linear_matches_two_step(cuda_lib):
+    import yan_b200
+    a, b = ref.make_inputs(256, 1024, 1024, seed=0)
+    rhs = ref.per_block_cast_to_fp8(b)
+    rhs_d = (rhs[0].cuda(), rhs[1].cuda())
+    out = yan_b200.fp8_linear(a.cuda(), rhs_d)
+    lhs = ref.per_token_cast_to_fp8(a)
+    _check(out.cpu(), ref.ref_gemm(lhs, rhs), "fp8_linear")
+
+
+def test_gemm_rejects_bad_arguments(cuda_lib):
+    import ctypes
+    from yan_b200 import _lib
+    t = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    p = t.data_ptr()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    f = "yan_b200_gemm_fp8_fp8_bf16_nt"
+    assert _lib.call_rc(f, p, p, p, p, p, 128, 128, 100, 128, stream, sms, 0) == 1      # K % 128
+    assert _lib.call_rc(f, p, p, p, p, p, 128, 128, 128, 64, stream, sms, 0) == 1       # ldd < N
+    assert _lib.call_rc(f, p, p, p, p, p, 128, 128, 128, 128, stream, sms + 1, 0) == 1  # too many SMs
+    assert _lib.call_rc(f, p, p, p, p, p, 128, 128, 128, 128, stream, sms, 48) == 1     # unknown tile
+    assert _lib.call_rc(f, p + 8, p, p, p, p, 128, 128, 128, 128, stream, sms, 0) == 1  # misaligned lhs
+    assert _lib.call_rc(f, None, p, p, p, p, 128, 128, 128, 128, stream, sms, 0) == 1   # null
+    assert _lib.call_rc(f, p, p, p, p, p, 0, 128, 128, 128, stream, sms, 0) == 1        # empty M

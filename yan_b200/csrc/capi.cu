@@ -1,0 +1,237 @@
+// C ABI of the FP8 fine-grained-scaled GEMM path (declarations and layouts: include/yan_b200.h).
+// Every entry point validates on the host, enqueues on the caller's stream and reports through
+// `return_code`; nothing allocates, frees or synchronises (except the explicit status read).
+
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "../../include/yan_b200.h"
+#include "gemm_dispatch.h"
+#include "quant/fp8_cast.cuh"
+
+namespace {
+
+// One status word per device image of this library; kernels report bounded-wait expiry here.
+__device__ int g_status_word = 0;
+
+unsigned long long g_timeout_ns = 2000000000ull;
+
+constexpr int kMaxDevices = 64;
+int* g_status_ptr[kMaxDevices] = {};
+
+int* status_word_of_current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    if (g_status_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        g_status_ptr[dev] = static_cast<int*>(p);
+    }
+    return g_status_ptr[dev];
+}
+
+inline void set_rc(int* rc, int v) {
+    if (rc != nullptr) *rc = v;
+}
+
+// Picks BLOCK_N by a wave model: cost = waves * (BLOCK_N + 64); the constant stands for the A tile and
+// the fixed per-tile work.  Large problems get 256 (fewest shared-memory bytes per flop), skinny ones
+// a narrower tile so that more SMs stream B.
+int choose_block_n(int m, int n, int num_sms) {
+    const int candidates[4] = {256, 128, 64, 32};
+    int best = 256;
+    long best_cost = -1;
+    for (int bn : candidates) {
+        if (bn > 32 && n < bn) continue;
+        const long tiles = static_cast<long>((m + 127) / 128) * ((n + bn - 1) / bn);
+        const long waves = (tiles + num_sms - 1) / num_sms;
+        const long cost = waves * (bn + 64);
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best = bn;
+        }
+    }
+    return best;
+}
+
+int dispatch_gemm(yan::GemmType type, yan::OutKind out_kind, yan::GemmArgs& a, int block_n, void* stream) {
+    if (a.m == 0 || a.n == 0 || a.k == 0) return yan::kBadArgument;
+    if (a.num_sms <= 0) return yan::kBadArgument;
+    if (block_n == 0) {
+        const int rows = (type == yan::GemmType::GroupedMasked) ? static_cast<int>(a.m * a.num_groups) : static_cast<int>(a.m);
+        block_n = choose_block_n(rows, static_cast<int>(a.n), a.num_sms);
+    }
+    a.status = status_word_of_current_device();
+    a.timeout_ns = g_timeout_ns;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (block_n) {
+        case 32: return yan::launch_gemm_bn32(type, out_kind, a, s);
+        case 64: return yan::launch_gemm_bn64(type, out_kind, a, s);
+        case 128: return yan::launch_gemm_bn128(type, out_kind, a, s);
+        case 256: return yan::launch_gemm_bn256(type, out_kind, a, s);
+        default: return yan::kBadArgument;
+    }
+}
+
+bool positive(int a, int b, int c) { return a > 0 && b > 0 && c > 0; }
+
+}  // namespace
+
+extern "C" {
+
+#define YAN_EXPORT __attribute__((visibility("default")))
+
+YAN_EXPORT int yan_b200_abi_version(void) { return YAN_B200_ABI_VERSION; }
+
+YAN_EXPORT const char* yan_b200_return_code_string(int code) {
+    switch (code) {
+        case YAN_B200_OK: return "ok";
+        case YAN_B200_BAD_ARGUMENT: return "bad argument (null/misaligned pointer, size, stride or K % 128 != 0)";
+        case YAN_B200_SMEM_TOO_LARGE: return "configuration needs more shared memory than the device offers";
+        case YAN_B200_TENSOR_MAP_FAILED: return "cuTensorMapEncodeTiled failed";
+        case YAN_B200_LAUNCH_FAILED: return "kernel launch or CUDA runtime call failed";
+        case YAN_B200_COMM_FAILED: return "collective communication failed";
+        case YAN_B200_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
+        case YAN_B200_WORKSPACE_TOO_SMALL: return "workspace too small";
+        default: return "unknown code";
+    }
+}
+
+YAN_EXPORT void yan_b200_gemm_fp8_fp8_bf16_nt(const void* lhs, const void* lhs_scales, const void* rhs,
+                                              const void* rhs_scales, void* out, int m, int n, int k, int ldd,
+                                              void* stream, int num_sms, int block_n, int* return_code) {
+    if (!positive(m, n, k) || ldd <= 0) return set_rc(return_code, yan::kBadArgument);
+    yan::GemmArgs a;
+    a.lhs = lhs;
+    a.lhs_scales = static_cast<const float*>(lhs_scales);
+    a.lhs_scales_ld = static_cast<uint32_t>(m);
+    a.rhs = rhs;
+    a.rhs_scales = static_cast<const float*>(rhs_scales);
+    a.out = out;
+    a.ldd = static_cast<uint32_t>(ldd);
+    a.m = m, a.n = n, a.k = k;
+    a.num_sms = num_sms;
+    set_rc(return_code, dispatch_gemm(yan::GemmType::Normal, yan::OutKind::BF16, a, block_n, stream));
+}
+
+YAN_EXPORT void yan_b200_gemm_fp8_fp8_f32_nt(const void* lhs, const void* lhs_scales, const void* rhs,
+                                             const void* rhs_scales, void* out, int m, int n, int k, int ldd,
+                                             void* stream, int num_sms, int block_n, int* return_code) {
+    if (!positive(m, n, k) || ldd <= 0) return set_rc(return_code, yan::kBadArgument);
+    yan::GemmArgs a;
+    a.lhs = lhs;
+    a.lhs_scales = static_cast<const float*>(lhs_scales);
+    a.lhs_scales_ld = static_cast<uint32_t>(m);
+    a.rhs = rhs;
+    a.rhs_scales = static_cast<const float*>(rhs_scales);
+    a.out = out;
+    a.ldd = static_cast<uint32_t>(ldd);
+    a.m = m, a.n = n, a.k = k;
+    a.num_sms = num_sms;
+    set_rc(return_code, dispatch_gemm(yan::GemmType::Normal, yan::OutKind::F32, a, block_n, stream));
+}
+
+YAN_EXPORT void yan_b200_m_grouped_gemm_fp8_fp8_bf16_nt_contiguous(const void* lhs, const void* lhs_scales,
+                                                                   const void* rhs, const void* rhs_scales, void* out,
+                                                                   const int* m_indices, int m, int n, int k,
+                                                                   int num_groups, void* stream, int num_sms,
+                                                                   int block_n, int* return_code) {
+    if (!positive(m, n, k) || num_groups <= 0 || m % 128 != 0) return set_rc(return_code, yan::kBadArgument);
+    yan::GemmArgs a;
+    a.lhs = lhs;
+    a.lhs_scales = static_cast<const float*>(lhs_scales);
+    a.lhs_scales_ld = static_cast<uint32_t>(m);
+    a.rhs = rhs;
+    a.rhs_scales = static_cast<const float*>(rhs_scales);
+    a.out = out;
+    a.ldd = static_cast<uint32_t>(n);
+    a.grouped_layout = m_indices;
+    a.m = m, a.n = n, a.k = k;
+    a.num_groups = static_cast<uint32_t>(num_groups);
+    a.num_sms = num_sms;
+    if (n % 128 != 0) return set_rc(return_code, yan::kBadArgument);
+    set_rc(return_code, dispatch_gemm(yan::GemmType::GroupedContiguous, yan::OutKind::BF16, a, block_n, stream));
+}
+
+YAN_EXPORT void yan_b200_m_grouped_gemm_fp8_fp8_bf16_nt_masked(const void* lhs, const void* lhs_scales, const void* rhs,
+                                                               const void* rhs_scales, void* out, const int* masked_m,
+                                                               int m_max, int n, int k, int num_groups, void* stream,
+                                                               int num_sms, int block_n, int* return_code) {
+    if (!positive(m_max, n, k) || num_groups <= 0 || n % 128 != 0) return set_rc(return_code, yan::kBadArgument);
+    yan::GemmArgs a;
+    a.lhs = lhs;
+    a.lhs_scales = static_cast<const float*>(lhs_scales);
+    a.lhs_scales_ld = static_cast<uint32_t>(m_max) * static_cast<uint32_t>(num_groups);
+    a.rhs = rhs;
+    a.rhs_scales = static_cast<const float*>(rhs_scales);
+    a.out = out;
+    a.ldd = static_cast<uint32_t>(n);
+    a.grouped_layout = masked_m;
+    a.m = m_max, a.n = n, a.k = k;
+    a.num_groups = static_cast<uint32_t>(num_groups);
+    a.num_sms = num_sms;
+    set_rc(return_code, dispatch_gemm(yan::GemmType::GroupedMasked, yan::OutKind::BF16, a, block_n, stream));
+}
+
+YAN_EXPORT void yan_b200_per_token_cast_to_fp8(const void* x, void* out, void* out_scales, int m, int k, int x_ld,
+                                               int scales_ld, void* stream, int* return_code) {
+    if (m <= 0 || k <= 0 || x_ld <= 0 || scales_ld <= 0) return set_rc(return_code, yan::kBadArgument);
+    set_rc(return_code,
+           yan::launch_per_token_cast_to_fp8(x, out, static_cast<float*>(out_scales), m, k, x_ld, scales_ld,
+                                             static_cast<cudaStream_t>(stream)));
+}
+
+YAN_EXPORT void yan_b200_per_block_cast_to_fp8(const void* w, void* out, void* out_scales, int n, int k, void* stream,
+                                               int* return_code) {
+    if (n <= 0 || k <= 0) return set_rc(return_code, yan::kBadArgument);
+    set_rc(return_code, yan::launch_per_block_cast_to_fp8(w, out, static_cast<float*>(out_scales), n, k,
+                                                          static_cast<cudaStream_t>(stream)));
+}
+
+YAN_EXPORT size_t yan_b200_fp8_linear_workspace_bytes(int m, int k) {
+    if (m <= 0 || k <= 0 || k % 128 != 0) return 0;
+    const size_t q_bytes = yan::align_up(static_cast<size_t>(m) * k, static_cast<size_t>(256));
+    const size_t s_bytes = yan::align_up(static_cast<size_t>(m) * (k / 128) * sizeof(float), static_cast<size_t>(256));
+    return q_bytes + s_bytes;
+}
+
+YAN_EXPORT void yan_b200_fp8_linear_bf16(const void* a, const void* rhs, const void* rhs_scales, void* out,
+                                         void* workspace, size_t workspace_bytes, int m, int n, int k, int ldd,
+                                         void* stream, int num_sms, int block_n, int* return_code) {
+    if (!positive(m, n, k) || k % 128 != 0 || workspace == nullptr) return set_rc(return_code, yan::kBadArgument);
+    if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0) return set_rc(return_code, yan::kBadArgument);
+    if (workspace_bytes < yan_b200_fp8_linear_workspace_bytes(m, k))
+        return set_rc(return_code, yan::kWorkspaceTooSmall);
+    uint8_t* q = static_cast<uint8_t*>(workspace);
+    float* scales = reinterpret_cast<float*>(q + yan::align_up(static_cast<size_t>(m) * k, static_cast<size_t>(256)));
+    int rc = yan::launch_per_token_cast_to_fp8(a, q, scales, m, k, k, m, static_cast<cudaStream_t>(stream));
+    if (rc != yan::kOk) return set_rc(return_code, rc);
+    yan_b200_gemm_fp8_fp8_bf16_nt(q, scales, rhs, rhs_scales, out, m, n, k, ldd, stream, num_sms, block_n, return_code);
+}
+
+YAN_EXPORT void yan_b200_read_device_status(int* status, int reset, int* return_code) {
+    if (status == nullptr) return set_rc(return_code, yan::kBadArgument);
+    int* word = status_word_of_current_device();
+    if (word == nullptr) return set_rc(return_code, yan::kLaunchFailed);
+    if (cudaMemcpy(status, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        cudaGetLastError();
+        return set_rc(return_code, yan::kLaunchFailed);
+    }
+    if (reset != 0 && *status != 0) {
+        const int zero = 0;
+        if (cudaMemcpy(word, &zero, sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess) {
+            cudaGetLastError();
+            return set_rc(return_code, yan::kLaunchFailed);
+        }
+    }
+    set_rc(return_code, yan::kOk);
+}
+
+YAN_EXPORT void yan_b200_set_wait_timeout_ns(unsigned long long timeout_ns) {
+    g_timeout_ns = timeout_ns == 0 ? 1 : timeout_ns;
+}
+
+}  // extern "C"

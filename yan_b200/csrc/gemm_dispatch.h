@@ -1,0 +1,22 @@
+#pragma once
+// Internal interface between the C-ABI translation unit and the per-BLOCK_N GEMM instantiation units
+// (gemm_inst.cu is compiled once per BLOCK_N so the instantiations build in parallel).
+#include <cuda_runtime.h>
+
+#include "gemm/fp8_gemm.cuh"
+
+namespace yan {
+
+enum class OutKind { BF16 = 0, F32 = 1 };
+
+int launch_gemm_bn32(GemmType type, OutKind out, const GemmArgs& args, cudaStream_t stream);
+int launch_gemm_bn64(GemmType type, OutKind out, const GemmArgs& args, cudaStream_t stream);
+int launch_gemm_bn128(GemmType type, OutKind out, const GemmArgs& args, cudaStream_t stream);
+int launch_gemm_bn256(GemmType type, OutKind out, const GemmArgs& args, cudaStream_t stream);
+
+// Default pipeline depth per BLOCK_N: as many 128-wide k-block stages as fit in 227 KB next to the barriers.
+constexpr uint32_t default_num_stages(uint32_t block_n) {
+    return block_n == 256 ? 4 : block_n == 128 ? 6 : 8;
+}
+
+}  // namespace yan

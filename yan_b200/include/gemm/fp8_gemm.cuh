@@ -1,0 +1,500 @@
+#pragma once
+// FP8 (e4m3) fine-grained-scaled GEMM for sm_100a:  D[M,N] (bf16 or fp32) = A[M,K] . B[N,K]^T with
+//   A scales: one fp32 per (row, 128-wide k-block), stored k-block-major (M contiguous)
+//   B scales: one fp32 per 128x128 block, [N/128, K/128] row-major.
+//
+// This is the kernel the reference leaves unfinished at yan/include/gemm/fp8_gemm.cuh:32-197
+// (persistent, warp-specialised, TMA-fed, per-k-block scale promotion), rebuilt for Blackwell:
+//   * operands: TMA 2D tiled loads (128-byte swizzle) into a kNumStages-deep shared-memory ring,
+//     each CTA loading its own tiles (no cluster multicast);
+//   * math: ONE thread issues `tcgen05.mma.kind::f8f6f4` 128 x BLOCK_N x 32; the first MMA of each
+//     128-wide k-block overwrites a TMEM accumulator buffer, so a buffer holds exactly one
+//     k-block's partial sum  P_kb = A8_kb . B8_kb^T;
+//   * promotion: two warpgroups read P_kb from TMEM (`tcgen05.ld`), multiply by
+//     sA[row,kb] * sB[n/128,kb] and accumulate in fp32 registers, while the MMA thread already
+//     fills the next TMEM buffer (2 or 4 buffers rotate);
+//   * epilogue: registers -> bf16 -> global (16-byte stores), overlapped with the next tile's MMAs.
+// Every mbarrier wait is bounded: on expiry the kernel records a code in a status word, all roles
+// drain, TMEM is freed and the kernel returns normally.
+
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+
+#include "mma_utils.cuh"
+#include "ptx.cuh"
+#include "scheduler.cuh"
+#include "tma_utils.cuh"
+#include "utils.cuh"
+
+namespace yan {
+
+constexpr uint32_t kBlockM = 128;
+constexpr uint32_t kBlockK = 128;
+
+// Device-side view of one launch.
+struct GemmParams {
+    const float* scales_a;      // [K/128][sa_ld], element (kb, row) at kb * sa_ld + row
+    const float* scales_b;      // [groups][ceil(N/128)][K/128]
+    const int* grouped_layout;  // Contiguous: [M] group per row (-1 = padding); Masked: [G] valid rows
+    void* out;                  // [rows][ldd]
+    uint32_t sa_ld;
+    uint32_t ldd;
+    uint32_t shape_m;  // Normal/Contiguous: total rows; Masked: rows per group (M_max)
+    uint32_t shape_n;
+    uint32_t shape_k;
+    uint32_t num_groups;
+    int* status;  // optional device word: 0 = fine, otherwise (kDeviceTimeout << 8) | site
+    unsigned long long timeout_ns;
+};
+
+namespace detail {
+
+// Wait on an mbarrier phase with a wall-clock bound.  Returns false when the wait ran out or another
+// role already gave up; the caller then leaves its loop.
+__device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                             const GemmParams& p, int site) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    uint32_t spins = 0;
+    while (!ptx::mbar_try_wait(bar, parity)) {
+        if ((++spins & 0x3Fu) == 0) {
+            if (*abort_flag != 0) return false;
+            if (ptx::globaltimer_ns() - t0 > p.timeout_ns) {
+                *abort_flag = 1;
+                if (p.status != nullptr) atomicCAS(p.status, 0, (static_cast<int>(kDeviceTimeout) << 8) | site);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+template <typename out_t, uint32_t kCols>
+__device__ __forceinline__ void store_row(out_t* dst, const float (&acc)[kCols], uint32_t n_first, uint32_t shape_n) {
+    if constexpr (sizeof(out_t) == 2) {
+#pragma unroll
+        for (uint32_t j = 0; j < kCols / 8; ++j) {
+            if (n_first + j * 8 < shape_n) {
+                uint4 v;
+                __nv_bfloat162 t0 = __floats2bfloat162_rn(acc[j * 8 + 0], acc[j * 8 + 1]);
+                __nv_bfloat162 t1 = __floats2bfloat162_rn(acc[j * 8 + 2], acc[j * 8 + 3]);
+                __nv_bfloat162 t2 = __floats2bfloat162_rn(acc[j * 8 + 4], acc[j * 8 + 5]);
+                __nv_bfloat162 t3 = __floats2bfloat162_rn(acc[j * 8 + 6], acc[j * 8 + 7]);
+                v.x = *reinterpret_cast<uint32_t*>(&t0);
+                v.y = *reinterpret_cast<uint32_t*>(&t1);
+                v.z = *reinterpret_cast<uint32_t*>(&t2);
+                v.w = *reinterpret_cast<uint32_t*>(&t3);
+                *reinterpret_cast<uint4*>(dst + j * 8) = v;
+            }
+        }
+    } else {
+#pragma unroll
+        for (uint32_t j = 0; j < kCols / 4; ++j) {
+            if (n_first + j * 4 < shape_n) {
+                float4 v = make_float4(acc[j * 4 + 0], acc[j * 4 + 1], acc[j * 4 + 2], acc[j * 4 + 3]);
+                *reinterpret_cast<float4*>(dst + j * 4) = v;
+            }
+        }
+    }
+}
+
+}  // namespace detail
+
+template <uint32_t BLOCK_N, uint32_t kNumStages>
+struct GemmSmemLayout {
+    static constexpr uint32_t kNumTmemBufs = (BLOCK_N >= 256) ? 2 : 4;
+    static constexpr uint32_t kTmemCols = kNumTmemBufs * BLOCK_N;
+    static constexpr uint32_t SMEM_A_SIZE_PER_STAGE = kBlockM * kBlockK;
+    static constexpr uint32_t SMEM_B_SIZE_PER_STAGE = BLOCK_N * kBlockK;
+    static constexpr uint32_t kOffA = 0;
+    static constexpr uint32_t kOffB = kOffA + kNumStages * SMEM_A_SIZE_PER_STAGE;
+    static constexpr uint32_t kOffBarriers = kOffB + kNumStages * SMEM_B_SIZE_PER_STAGE;
+    static constexpr uint32_t kNumBarriers = 2 * kNumStages + 2 * kNumTmemBufs;
+    static constexpr uint32_t kOffTmemSlot = kOffBarriers + kNumBarriers * 8;
+    static constexpr uint32_t kOffAbort = kOffTmemSlot + 4;
+    // +1024: the dynamic shared-memory base is re-aligned to 1024 bytes inside the kernel.
+    static constexpr uint32_t kSmemSize = kOffAbort + 4 + 1024;
+    static_assert(kTmemCols == 32 || kTmemCols == 64 || kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512,
+                  "TMEM allocations are powers of two between 32 and 512 columns");
+    static_assert(BLOCK_N % 32 == 0 && BLOCK_N >= 32 && BLOCK_N <= 256, "UMMA M=128 needs N % 16 == 0, N <= 256");
+};
+
+template <uint32_t BLOCK_N, uint32_t kNumStages, GemmType kGemmType, typename out_t>
+__global__ void __launch_bounds__(get_num_threads_per_sm<>(kBlockM), 1)
+    fp8_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tensor_map_a,
+                    const __grid_constant__ CUtensorMap tensor_map_b) {
+#if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ >= 1000)
+    using L = GemmSmemLayout<BLOCK_N, kNumStages>;
+    using Sched = Scheduler<kGemmType, kBlockM, BLOCK_N>;
+    constexpr uint32_t kNumTmemBufs = L::kNumTmemBufs;
+    constexpr uint32_t kColsPerWG = BLOCK_N / 2;
+    constexpr uint32_t kNumMathWarps = 8;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
+
+    uint64_t* full_barriers = reinterpret_cast<uint64_t*>(smem + L::kOffBarriers);
+    uint64_t* empty_barriers = full_barriers + kNumStages;
+    uint64_t* tmem_full_barriers = empty_barriers + kNumStages;
+    uint64_t* tmem_empty_barriers = tmem_full_barriers + kNumTmemBufs;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kOffTmemSlot);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kOffAbort);
+
+    const uint32_t warp_idx = __shfl_sync(0xffffffffu, threadIdx.x / 32, 0);
+    const uint32_t lane_idx = ptx::lane_id();
+    const uint32_t num_k_blocks = p.shape_k / kBlockK;
+    const uint32_t num_sb_rows = ceil_div(p.shape_n, 128u);
+
+    if (warp_idx == 0 && lane_idx == 0) {
+        ptx::tma_prefetch_desc(&tensor_map_a);
+        ptx::tma_prefetch_desc(&tensor_map_b);
+    }
+    if (warp_idx == 1 && lane_idx == 0) {
+#pragma unroll
+        for (uint32_t i = 0; i < kNumStages; ++i) {
+            ptx::mbar_init(full_barriers + i, 1);   // producer's arrive.expect_tx
+            ptx::mbar_init(empty_barriers + i, 1);  // tcgen05.commit of the MMA thread
+        }
+#pragma unroll
+        for (uint32_t i = 0; i < kNumTmemBufs; ++i) {
+            ptx::mbar_init(tmem_full_barriers + i, 1);               // tcgen05.commit
+            ptx::mbar_init(tmem_empty_barriers + i, kNumMathWarps);  // one arrival per promotion warp
+        }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async_smem();
+    }
+    if (warp_idx == 2) {
+        ptx::tmem_alloc(tmem_slot, L::kTmemCols);
+        ptx::tmem_relinquish_alloc_permit();
+    }
+    ptx::tcgen05_fence_before_thread_sync();
+    __syncthreads();
+    ptx::tcgen05_fence_after_thread_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp_idx < 4) {
+        ptx::reg_dealloc<kNumControlRegisters>();
+
+        if (warp_idx == 0 && lane_idx == 0) {
+            // ------------------------------ TMA producer ------------------------------
+            Sched sched(p.shape_m, p.shape_n, p.grouped_layout, p.num_groups);
+            uint32_t m_block_idx, n_block_idx, stage = 0, phase = 0;
+            bool alive = true;
+            while (alive && sched.get_next_block(m_block_idx, n_block_idx)) {
+                const int group = sched.get_group(m_block_idx);
+                if (group < 0) continue;
+                const int32_t a_row = static_cast<int32_t>(sched.get_row_base(m_block_idx));
+                const int32_t b_row = static_cast<int32_t>(group * p.shape_n + n_block_idx * BLOCK_N);
+                for (uint32_t kb = 0; kb < num_k_blocks; ++kb) {
+                    if (!detail::bounded_wait(empty_barriers + stage, phase ^ 1, abort_flag, p, 1)) {
+                        alive = false;
+                        break;
+                    }
+                    ptx::mbar_arrive_expect_tx(full_barriers + stage,
+                                               L::SMEM_A_SIZE_PER_STAGE + L::SMEM_B_SIZE_PER_STAGE);
+                    ptx::tma_load_2d(smem + L::kOffA + stage * L::SMEM_A_SIZE_PER_STAGE, &tensor_map_a,
+                                     full_barriers + stage, static_cast<int32_t>(kb * kBlockK), a_row);
+                    ptx::tma_load_2d(smem + L::kOffB + stage * L::SMEM_B_SIZE_PER_STAGE, &tensor_map_b,
+                                     full_barriers + stage, static_cast<int32_t>(kb * kBlockK), b_row);
+                    if (++stage == kNumStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+            if (!alive) {
+                // Give copies still in flight time to land before the CTA's shared memory is released.
+                const uint64_t t0 = ptx::globaltimer_ns();
+                while (ptx::globaltimer_ns() - t0 < 1000000ull) __nanosleep(1000);
+            }
+        } else if (warp_idx == 1 && lane_idx == 0) {
+            // ------------------------------ MMA issuer ------------------------------
+            Sched sched(p.shape_m, p.shape_n, p.grouped_layout, p.num_groups);
+            constexpr uint32_t idesc = make_instr_desc_e4m3_f32(kBlockM, BLOCK_N);
+            uint32_t m_block_idx, n_block_idx, stage = 0, phase = 0, buf = 0, buf_phase = 0;
+            bool alive = true;
+            while (alive && sched.get_next_block(m_block_idx, n_block_idx)) {
+                if (sched.get_group(m_block_idx) < 0) continue;
+                for (uint32_t kb = 0; kb < num_k_blocks; ++kb) {
+                    if (!detail::bounded_wait(full_barriers + stage, phase, abort_flag, p, 2) ||
+                        !detail::bounded_wait(tmem_empty_barriers + buf, buf_phase ^ 1, abort_flag, p, 3)) {
+                        alive = false;
+                        break;
+                    }
+                    ptx::tcgen05_fence_after_thread_sync();
+                    const uint64_t a_desc =
+                        make_smem_desc_k_major_sw128(ptx::smem_u32(smem + L::kOffA + stage * L::SMEM_A_SIZE_PER_STAGE));
+                    const uint64_t b_desc =
+                        make_smem_desc_k_major_sw128(ptx::smem_u32(smem + L::kOffB + stage * L::SMEM_B_SIZE_PER_STAGE));
+                    const uint32_t tmem_d = tmem_base + buf * BLOCK_N;
+#pragma unroll
+                    for (uint32_t k = 0; k < kBlockK / kUmmaK; ++k)
+                        ptx::umma_f8f6f4_ss(tmem_d, a_desc + k * kDescKStep, b_desc + k * kDescKStep, idesc, k > 0);
+                    ptx::umma_commit(empty_barriers + stage);      // smem stage reusable once these MMAs are done
+                    ptx::umma_commit(tmem_full_barriers + buf);    // partial sum of this k-block is complete
+                    if (++stage == kNumStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                    if (++buf == kNumTmemBufs) {
+                        buf = 0;
+                        buf_phase ^= 1;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------ promotion + epilogue warpgroups ------------------------------
+        ptx::reg_alloc<kNumMathRegisters>();
+
+        const uint32_t wg = (warp_idx - 4) / 4;
+        const uint32_t quarter = warp_idx % 4;
+        const uint32_t row_in_tile = quarter * 32 + lane_idx;
+        const uint32_t col0 = wg * kColsPerWG;
+        const uint32_t tmem_lane_base = tmem_base + ((quarter * 32u) << 16) + col0;
+
+        Sched sched(p.shape_m, p.shape_n, p.grouped_layout, p.num_groups);
+        uint32_t m_block_idx, n_block_idx, buf = 0, buf_phase = 0;
+        bool alive = true;
+        float acc[kColsPerWG];
+
+        while (alive && sched.get_next_block(m_block_idx, n_block_idx)) {
+            const int group = sched.get_group(m_block_idx);
+            if (group < 0) continue;
+            const uint32_t row = sched.get_row_base(m_block_idx) + row_in_tile;
+            const bool row_ok = row < sched.get_row_limit();
+            const uint32_t n_first = n_block_idx * BLOCK_N + col0;
+            const uint32_t sb_row = min(n_first / 128u, num_sb_rows - 1);
+            const float* sa_ptr = p.scales_a + row;
+            const float* sb_ptr = p.scales_b + (static_cast<size_t>(group) * num_sb_rows + sb_row) * num_k_blocks;
+
+            float sa_next = row_ok ? __ldg(sa_ptr) : 0.0f;
+            float sb_next = __ldg(sb_ptr);
+            for (uint32_t kb = 0; kb < num_k_blocks; ++kb) {
+                const float scale = sa_next * sb_next;
+                if (kb + 1 < num_k_blocks) {
+                    sa_next = row_ok ? __ldg(sa_ptr + static_cast<size_t>(kb + 1) * p.sa_ld) : 0.0f;
+                    sb_next = __ldg(sb_ptr + kb + 1);
+                }
+                const bool ok = detail::bounded_wait(tmem_full_barriers + buf, buf_phase, abort_flag, p, 4);
+                if (!__all_sync(0xffffffffu, ok)) {
+                    alive = false;
+                    break;
+                }
+                ptx::tcgen05_fence_after_thread_sync();
+                const uint32_t taddr = tmem_lane_base + buf * BLOCK_N;
+                if constexpr (kColsPerWG % 64 == 0) {
+#pragma unroll
+                    for (uint32_t c = 0; c < kColsPerWG / 64; ++c) {
+                        uint32_t r[64];
+                        ptx::tmem_ld_32x32b_x64_wait(taddr + c * 64, r);
+                        if (kb == 0) {
+#pragma unroll
+                            for (uint32_t j = 0; j < 64; ++j) acc[c * 64 + j] = scale * __uint_as_float(r[j]);
+                        } else {
+#pragma unroll
+                            for (uint32_t j = 0; j < 64; ++j)
+                                acc[c * 64 + j] = fmaf(scale, __uint_as_float(r[j]), acc[c * 64 + j]);
+                        }
+                    }
+                } else if constexpr (kColsPerWG == 32) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32b_x32_wait(taddr, r);
+#pragma unroll
+                    for (uint32_t j = 0; j < 32; ++j)
+                        acc[j] = (kb == 0) ? scale * __uint_as_float(r[j]) : fmaf(scale, __uint_as_float(r[j]), acc[j]);
+                } else {
+                    static_assert(kColsPerWG == 16 || kColsPerWG % 64 == 0 || kColsPerWG == 32, "unsupported BLOCK_N");
+                    uint32_t r[16];
+                    ptx::tmem_ld_32x32b_x16_wait(taddr, r);
+#pragma unroll
+                    for (uint32_t j = 0; j < 16; ++j)
+                        acc[j] = (kb == 0) ? scale * __uint_as_float(r[j]) : fmaf(scale, __uint_as_float(r[j]), acc[j]);
+                }
+                // All of this warp's TMEM reads of the buffer are complete: hand it back to the MMA thread.
+                ptx::tcgen05_fence_before_thread_sync();
+                __syncwarp();
+                if (lane_idx == 0) ptx::mbar_arrive(tmem_empty_barriers + buf);
+                if (++buf == kNumTmemBufs) {
+                    buf = 0;
+                    buf_phase ^= 1;
+                }
+            }
+            if (alive && row_ok) {
+                out_t* dst = reinterpret_cast<out_t*>(p.out) + static_cast<size_t>(row) * p.ldd + n_first;
+                detail::store_row<out_t, kColsPerWG>(dst, acc, n_first, p.shape_n);
+            }
+        }
+        __syncwarp();
+    }
+
+    // Every role has left its loop (normally or through the bounded-wait path): free tensor memory.
+    ptx::tcgen05_fence_before_thread_sync();
+    __syncthreads();
+    if (warp_idx == 2) {
+        ptx::tcgen05_fence_after_thread_sync();
+        ptx::tmem_dealloc(tmem_base, L::kTmemCols);
+    }
+#endif
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+struct GemmArgs {
+    const void* lhs = nullptr;         // e4m3 [rows, K]
+    const float* lhs_scales = nullptr; // k-block-major, leading dimension lhs_scales_ld (>= rows)
+    uint32_t lhs_scales_ld = 0;
+    const void* rhs = nullptr;         // e4m3 [groups * N, K]
+    const float* rhs_scales = nullptr; // [groups, ceil(N/128), K/128]
+    void* out = nullptr;               // [rows, ldd]
+    uint32_t ldd = 0;
+    const int* grouped_layout = nullptr;
+    uint32_t m = 0, n = 0, k = 0, num_groups = 1;
+    int num_sms = 0;
+    int* status = nullptr;
+    unsigned long long timeout_ns = 2000000000ull;
+};
+
+inline bool is_aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+template <uint32_t BLOCK_N, uint32_t kNumStages, GemmType kGemmType, typename out_t>
+struct GemmLauncher {
+    using L = GemmSmemLayout<BLOCK_N, kNumStages>;
+    static constexpr uint32_t kSmemSize = L::kSmemSize;
+
+    static int launch(const GemmArgs& a, cudaStream_t stream) {
+        if (a.lhs == nullptr || a.lhs_scales == nullptr || a.rhs == nullptr || a.rhs_scales == nullptr ||
+            a.out == nullptr)
+            return kBadArgument;
+        if (a.m == 0 || a.n == 0 || a.k == 0 || a.k % kBlockK != 0 || a.n % 16 != 0 || a.num_groups == 0)
+            return kBadArgument;
+        constexpr uint32_t kVec = 16 / sizeof(out_t);
+        if (a.ldd < a.n || a.ldd % kVec != 0 || a.lhs_scales_ld == 0) return kBadArgument;
+        if (!is_aligned(a.lhs, 16) || !is_aligned(a.rhs, 16) || !is_aligned(a.out, 16) || !is_aligned(a.lhs_scales, 4) ||
+            !is_aligned(a.rhs_scales, 4))
+            return kBadArgument;
+        if (kGemmType != GemmType::Normal && a.grouped_layout == nullptr) return kBadArgument;
+        if (kGemmType == GemmType::Normal && a.num_groups != 1) return kBadArgument;
+        if (a.num_sms <= 0) return kBadArgument;
+
+        int device = 0, max_smem = 0, sm_count = 0;
+        if (cudaGetDevice(&device) != cudaSuccess) return kLaunchFailed;
+        cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+        if (static_cast<int>(kSmemSize) > max_smem) return kSmemTooLarge;
+        if (a.num_sms > sm_count) return kBadArgument;
+
+        const uint64_t a_rows =
+            (kGemmType == GemmType::GroupedMasked) ? static_cast<uint64_t>(a.m) * a.num_groups : a.m;
+        const uint64_t b_rows = static_cast<uint64_t>(a.n) * a.num_groups;
+        if (a_rows > 0x7fffffffull || b_rows > 0x7fffffffull) return kBadArgument;
+        if (kGemmType == GemmType::GroupedMasked ? a.lhs_scales_ld < a_rows : a.lhs_scales_ld < a.m)
+            return kBadArgument;
+
+        bool ok = true;
+        const CUtensorMap map_a = make_2d_tma_desc_u8_sw128(a.lhs, a_rows, a.k, a.k, kBlockM, ok);
+        const CUtensorMap map_b = make_2d_tma_desc_u8_sw128(a.rhs, b_rows, a.k, a.k, BLOCK_N, ok);
+        if (!ok) return kTensorMapFailed;
+
+        GemmParams p;
+        p.scales_a = a.lhs_scales;
+        p.scales_b = a.rhs_scales;
+        p.grouped_layout = a.grouped_layout;
+        p.out = a.out;
+        p.sa_ld = a.lhs_scales_ld;
+        p.ldd = a.ldd;
+        p.shape_m = a.m;
+        p.shape_n = a.n;
+        p.shape_k = a.k;
+        p.num_groups = a.num_groups;
+        p.status = a.status;
+        p.timeout_ns = a.timeout_ns;
+
+        auto kernel = fp8_gemm_kernel<BLOCK_N, kNumStages, kGemmType, out_t>;
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemSize) != cudaSuccess) {
+            cudaGetLastError();
+            return kSmemTooLarge;
+        }
+        uint32_t grid = static_cast<uint32_t>(a.num_sms);
+        if (kGemmType != GemmType::GroupedMasked) {
+            const uint32_t tiles = ceil_div(a.m, kBlockM) * ceil_div(a.n, BLOCK_N);
+            grid = tiles < grid ? tiles : grid;
+        }
+        kernel<<<grid, get_num_threads_per_sm<>(kBlockM), kSmemSize, stream>>>(p, map_a, map_b);
+        return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
+// `Gemm<...>`: the host class the reference's launch template instantiates but never defines
+// (yan/jit_kernels/gemm.py:20-30).  Template parameter order and the member names are the
+// template's; kNumTMAMulticast is accepted for source compatibility and must be 1 (this kernel
+// never multicasts).  The scale and output "descriptors" carry plain pointers because the kernel
+// reads scales with ordinary loads and writes D with 16-byte stores.
+// ---------------------------------------------------------------------------------------------
+struct ScalesADesc {
+    const float* ptr;
+    uint32_t ld;
+};
+struct OutDesc {
+    __nv_bfloat16* ptr;
+    uint32_t ld;
+};
+
+template <uint32_t SHAPE_N, uint32_t SHAPE_K, uint32_t BLOCK_M, uint32_t BLOCK_N, uint32_t BLOCK_K, uint32_t kNumGroups,
+          uint32_t kNumStages, uint32_t kNumTMAMulticast, GemmType kGemmType>
+class Gemm {
+    static_assert(BLOCK_M == kBlockM && BLOCK_K == kBlockK, "this kernel is built around 128 x BLOCK_N x 128 tiles");
+    static_assert(kNumTMAMulticast == 1, "cluster multicast is not used by this kernel");
+    static_assert(SHAPE_K % BLOCK_K == 0, "K must be a multiple of 128");
+
+public:
+    using Launcher = GemmLauncher<BLOCK_N, kNumStages, kGemmType, __nv_bfloat16>;
+    static constexpr uint32_t kSmemSize = Launcher::kSmemSize;
+
+    struct TmaDesc {
+        const void* ptr;
+        uint32_t rows;
+    };
+
+    template <typename T>
+    static TmaDesc make_2d_tma_a_desc(T* lhs, uint32_t m) {
+        return {lhs, m};
+    }
+    template <typename T>
+    static TmaDesc make_2d_tma_b_desc(T* rhs) {
+        return {rhs, SHAPE_N * kNumGroups};
+    }
+    static ScalesADesc make_2d_tma_scales_a_desc(const float* lhs_scales, uint32_t m) { return {lhs_scales, m}; }
+    static OutDesc make_2d_tma_d_desc(__nv_bfloat16* out, uint32_t /*m*/) { return {out, SHAPE_N}; }
+
+    // Returns a ReturnCode; the generated `launch` stores it in `__return_code`.
+    static int run(__nv_bfloat16* out, float* rhs_scales, int* grouped_layout, uint32_t m, const TmaDesc& a_desc,
+                   const TmaDesc& b_desc, const ScalesADesc& scales_a_desc, const OutDesc& d_desc, cudaStream_t stream,
+                   int num_sms, uint32_t smem_size) {
+        if (smem_size != 0 && smem_size < kSmemSize) return kSmemTooLarge;
+        GemmArgs a;
+        a.lhs = a_desc.ptr;
+        a.lhs_scales = scales_a_desc.ptr;
+        a.lhs_scales_ld = scales_a_desc.ld;
+        a.rhs = b_desc.ptr;
+        a.rhs_scales = rhs_scales;
+        a.out = out;
+        a.ldd = d_desc.ld;
+        a.grouped_layout = grouped_layout;
+        a.m = m;
+        a.n = SHAPE_N;
+        a.k = SHAPE_K;
+        a.num_groups = kNumGroups;
+        a.num_sms = num_sms;
+        return Launcher::launch(a, stream);
+    }
+};
+
+}  // namespace yan

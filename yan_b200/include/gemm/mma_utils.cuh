@@ -1,0 +1,68 @@
+#pragma once
+// UMMA (tcgen05.mma) descriptor construction and the CTA role layout.
+// Takes the place of the reference's WGMMA selector and thread-count helpers
+// (yan/include/gemm/mma_utils.cuh:17-84): instead of one 64xNx32 WGMMA atom per math
+// warpgroup writing registers, ONE thread issues 128xNx32 `kind::f8f6f4` MMAs whose fp32
+// accumulator lives in tensor memory; the math warpgroups become promotion warpgroups.
+
+#include <cstdint>
+
+#include "utils.cuh"
+
+namespace yan {
+
+// --- CTA role layout -------------------------------------------------------------------------
+// warp 0      : TMA producer (one elected lane)
+// warp 1      : MMA issuer   (one elected lane)
+// warp 2      : TMEM allocator / deallocator
+// warp 3      : spare (keeps the first four warps a full warpgroup for setmaxnreg)
+// warps 4..11 : two promotion/epilogue warpgroups; warpgroup h owns output columns
+//               [h*BLOCK_N/2, (h+1)*BLOCK_N/2) of the tile, warp (w%4) owns TMEM lanes 32*(w%4)..+31.
+constexpr uint32_t kNumControlThreads = 128;
+constexpr uint32_t kNumMathThreadsPerGroup = 128;
+
+__host__ __device__ constexpr int get_num_math_warpgroups(int /*block_m*/) { return 2; }
+
+template <uint32_t kNumTMAThreads = kNumControlThreads, uint32_t kNumMathThreads = kNumMathThreadsPerGroup>
+__host__ __device__ constexpr int get_num_threads_per_sm(int block_m) {
+    static_assert(kNumMathThreads == 128, "a promotion warpgroup is 128 threads (4 TMEM lane quarters)");
+    return get_num_math_warpgroups(block_m) * kNumMathThreads + kNumTMAThreads;
+}
+
+// Registers after setmaxnreg: 128*40 + 256*232 = 64512 <= 65536 (same split as fp8_gemm.cuh:171-172).
+constexpr uint32_t kNumControlRegisters = 40;
+constexpr uint32_t kNumMathRegisters = 232;
+
+// --- instruction descriptor (32 bit) for tcgen05.mma kind::f8f6f4 ------------------------------
+//  [4,6)  accumulator format: 1 = fp32
+//  [7,10) A format: 0 = e4m3      [10,13) B format: 0 = e4m3
+//  [15]   A major: 0 = K-major    [16]    B major: 0 = K-major
+//  [17,23) N >> 3                 [24,29) M >> 4
+__host__ __device__ constexpr uint32_t make_instr_desc_e4m3_f32(uint32_t umma_m, uint32_t umma_n) {
+    return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) | ((umma_n >> 3) << 17) | ((umma_m >> 4) << 24);
+}
+
+// --- shared-memory matrix descriptor (64 bit), K-major operand, 128-byte swizzle ---------------
+// The tile is rows x 128 bytes, written by TMA with CU_TENSOR_MAP_SWIZZLE_128B into a 1024-byte
+// aligned buffer: 8 rows form one 1024-byte swizzle atom.
+//  [0,14)  start address >> 4
+//  [16,30) leading-dimension byte offset >> 4 (unused for swizzled K-major; canonical value 1)
+//  [32,46) stride byte offset >> 4 = 1024 >> 4 (distance between 8-row groups)
+//  [46,48) descriptor version = 1 on sm_100
+//  [61,64) layout type: 2 = SWIZZLE_128B
+__device__ __forceinline__ uint64_t make_smem_desc_k_major_sw128(uint32_t smem_addr) {
+    uint64_t desc = 0;
+    desc |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    desc |= static_cast<uint64_t>(1) << 16;
+    desc |= static_cast<uint64_t>(1024 >> 4) << 32;
+    desc |= static_cast<uint64_t>(1) << 46;
+    desc |= static_cast<uint64_t>(2) << 61;
+    return desc;
+}
+
+// Advancing by one UMMA K step (32 e4m3 = 32 bytes) inside the 128-byte swizzle row adds
+// 32 >> 4 = 2 to the start-address field.
+constexpr uint32_t kUmmaK = 32;
+constexpr uint32_t kDescKStep = (kUmmaK * 1) >> 4;
+
+}  // namespace yan
