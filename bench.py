@@ -1,0 +1,440 @@
+#!/usr/bin/env python
+"""Benchmark of the FP8 fine-grained-scaled GEMM path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Workload (every N): the column-parallel prefill GEMM  M=8192, N=28672, K=8192, e4m3 operands with
+1x128 / 128x128 fp32 scales, bf16 output.  B is sharded along N over the ranks, A is replicated, no
+collective is on the data path; total work is fixed, so scaling is "strong".
+One step = quantize A (bf16 -> e4m3 + scales) followed by the GEMM over this rank's N/g columns.
+Inputs are seeded synthetic tensors with the workload's shapes and distributions (A ~ N(0,1),
+B ~ N(0, 0.02)); no dataset is involved.
+
+Printed: ONE JSON line (rank 0).  `value` = 2*M*N*K / (max-over-ranks device time per step), inputs
+resident in HBM.  `e2e` = the same step through the public API with A in pinned host memory and D read
+back to the host every step.  `roofline` is for the GEMM kernel alone (CUDA events around each launch
+on the launching stream).  `cpu_baseline` times the CPU oracle on a bounded slab on rank 0 at N=1.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+M, N, K = 8192, 28672, 8192
+WORKLOAD = "C4 column-parallel prefill GEMM M=8192 N=28672 K=8192 (B sharded along N, A replicated)"
+METRIC = "FP8 GEMM TFLOP/s (% FP8 peak); small-M HBM GB/s; 1/2/4/8-GPU scaling"
+CPU_SLAB_ROWS = 256
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int) -> None:
+        self.rows = []
+        self.proc = None
+        self.thread = None
+        self.device_index = device_index
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.device_index), "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self) -> None:
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.strip().split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, r[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        return rank, world, local, dist
+    assert n_gpus == 1, "launch with torch.distributed.run for --gpus > 1"
+    torch.cuda.set_device(0)
+    return 0, 1, 0, None
+
+
+def make_device_inputs(m, n_local, k, rank, outliers=False):
+    """Seeded synthetic operands created on the device (identical A on every rank, rank-specific B shard)."""
+    import yan_b200
+    g = torch.Generator(device="cuda").manual_seed(0)
+    a = torch.randn(m, k, generator=g, device="cuda", dtype=torch.float32)
+    if outliers:
+        cols = torch.randperm(k, generator=torch.Generator().manual_seed(0))[: k // 100].cuda()
+        a[:, cols] *= 20.0
+    a = a.to(torch.bfloat16)
+    gb = torch.Generator(device="cuda").manual_seed(1000 + rank)
+    b = (torch.randn(n_local, k, generator=gb, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    rhs = yan_b200.per_block_cast_to_fp8(b)
+    del b
+    return a, rhs
+
+
+def time_graph_replays(fn, replays: int, launches_per_graph: int) -> float:
+    """Seconds per launch of `fn` captured `launches_per_graph` times in a CUDA graph (removes CPU launch gaps)."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        fn()
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(launches_per_graph):
+            fn(i)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / 1e3 / (replays * launches_per_graph)
+
+
+def bench_decode(m: int, peaks) -> dict:
+    """Small-M weight-streaming GEMM (N=7168, K=2048): HBM-bound.  Rotates over enough distinct operand
+    sets that consecutive launches never find their B in L2 (total footprint >= 2 x L2)."""
+    import yan_b200
+    n, k = 7168, 2048
+    l2 = torch.cuda.get_device_properties(0).L2_cache_size
+    per_set = n * k + m * k + 2 * m * n
+    sets = max(4, -(-2 * l2 // per_set))
+    a, _ = make_device_inputs(m, 128, k, 0, outliers=True)
+    lhs = yan_b200.per_token_cast_to_fp8(a)
+    rhs_list, outs = [], []
+    for i in range(sets):
+        _, rhs = make_device_inputs(m, n, k, 100 + i)
+        rhs_list.append(rhs)
+        outs.append(torch.empty(m, n, dtype=torch.bfloat16, device="cuda"))
+
+    def fn(i=0):
+        yan_b200.gemm_fp8_fp8_bf16_nt(lhs, rhs_list[i % sets], outs[i % sets])
+
+    t = time_graph_replays(fn, replays=20, launches_per_graph=sets)
+    algo_bytes = m * k + 4 * m * (k // 128) + n * k + 4 * (n // 128) * (k // 128) + 2 * m * n
+    gbs = algo_bytes / t / 1e9
+    return {"workload": f"C2 decode M={m} N={n} K={k}", "us": t * 1e6, "GB/s": gbs, "algorithmic_bytes": algo_bytes,
+            "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "frac_of_nominal_8TBs": gbs / 8000.0,
+            "timing": f"CUDA graph of {sets} launches over {sets} distinct B/D sets (>= 2 x L2), 20 replays"}
+
+
+def bench_dense(name: str, m: int, n: int, k: int, peaks, iters: int = 10) -> dict:
+    import yan_b200
+    from yan_b200.utils import bench_events
+    a, rhs = make_device_inputs(m, n, k, 0)
+    lhs = yan_b200.per_token_cast_to_fp8(a)
+    out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    t = bench_events(lambda: yan_b200.gemm_fp8_fp8_bf16_nt(lhs, rhs, out), num_tests=iters, flush_l2=True)
+    tq = bench_events(lambda: yan_b200.per_token_cast_to_fp8(a, out=lhs), num_tests=iters, flush_l2=True)
+    tf = 2.0 * m * n * k / t / 1e12
+    qbytes = 3 * m * k + 4 * m * (k // 128)
+    return {"workload": f"{name} M={m} N={n} K={k}", "gemm_us": t * 1e6, "TFLOP/s": tf,
+            "frac_of_2x_measured_bf16_burst": tf / (2 * peaks["bf16_tflops"]), "frac_of_nominal_4.5PF": tf / 4500.0,
+            "quant_us": tq * 1e6, "quant_GB/s": qbytes / tq / 1e9,
+            "quant_frac_of_measured_hbm": qbytes / tq / 1e9 / peaks["hbm_gbs"]}
+
+
+def cpu_reference_step(a_slab, rhs_cpu):
+    """The CPU dequantize-and-matmul path on one slab: quantize A, dequantize both, fp32 matmul, bf16."""
+    from oracle import ref
+    lhs = ref.per_token_cast_to_fp8(a_slab)
+    return ref.ref_gemm(lhs, rhs_cpu)
+
+
+def make_cpu_inputs():
+    from oracle import ref
+    g = torch.Generator().manual_seed(0)
+    a = torch.randn(CPU_SLAB_ROWS, K, generator=g).to(torch.bfloat16)
+    b = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+    rhs = ref.per_block_cast_to_fp8(b)
+    return a, rhs
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    a, rhs = make_cpu_inputs()
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_reference_step(a, rhs)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_reference_step(a, rhs)
+    dt = (time.perf_counter() - t0) / args.steps
+    flops = 2.0 * CPU_SLAB_ROWS * N * K
+    value = flops / dt / 1e12
+    cores = torch.get_num_threads()
+    sample = (f"{CPU_SLAB_ROWS}-row slab of A against the full B (N={N}, K={K}) per step: quantize A, dequantize A and B "
+              f"to fp32, torch.matmul fp32, round to bf16; flops counted for the slab only")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32 (dequantized e4m3)", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "M": M, "N": N, "K": K},
+            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args) -> None:
+    import yan_b200
+    peaks = load_peaks()
+    rank, world, local, dist = dist_setup(args.gpus)
+    assert N % (world * 256) == 0
+    n_local = N // world
+    dev_name = torch.cuda.get_device_name()
+
+    a, rhs = make_device_inputs(M, n_local, K, rank)
+    lhs = (torch.empty(M, K, dtype=torch.float8_e4m3fn, device="cuda"),
+           torch.empty(K // 128, M, dtype=torch.float32, device="cuda").t())
+    out = torch.empty(M, n_local, dtype=torch.bfloat16, device="cuda")
+
+    def step():
+        yan_b200.per_token_cast_to_fp8(a, out=lhs)
+        yan_b200.gemm_fp8_fp8_bf16_nt(lhs, rhs, out)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+
+    # ---- timed region: exactly K steps; per-kernel events on the launching (current) stream ----
+    sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.3)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    barrier()
+    t_start = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for i in range(args.steps):
+        ev[i][0].record()
+        yan_b200.per_token_cast_to_fp8(a, out=lhs)
+        ev[i][1].record()
+        yan_b200.gemm_fp8_fp8_bf16_nt(lhs, rhs, out)
+        ev[i][2].record()
+    t_end.record()
+    barrier()
+    clocks = sampler.stop()
+    elapsed_ms = t_start.elapsed_time(t_end)
+    quant_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
+    gemm_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
+    assert yan_b200.read_device_status() == 0, "a device-side wait ran out during the benchmark"
+    if dist is not None:
+        t = torch.tensor([elapsed_ms, gemm_ms, quant_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms, gemm_ms, quant_ms = t.tolist()
+    ms_per_step = elapsed_ms / args.steps
+    flops_total = 2.0 * M * N * K
+    value = flops_total / (ms_per_step / 1e3) / 1e12
+
+    # ---- end to end: A from pinned host memory, D back to pinned host memory, every step ----
+    a_host = a.cpu().pin_memory()
+    out_host = torch.empty(M, n_local, dtype=torch.bfloat16).pin_memory()
+    a_dev = torch.empty_like(a)
+
+    def e2e_step():
+        a_dev.copy_(a_host, non_blocking=True)
+        yan_b200.per_token_cast_to_fp8(a_dev, out=lhs)
+        yan_b200.gemm_fp8_fp8_bf16_nt(lhs, rhs, out)
+        out_host.copy_(out, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = t.item()
+    e2e_value = flops_total / (e2e_ms / 1e3) / 1e12
+
+    # ---- roofline of the dominant kernel (the GEMM) ----
+    gemm_flops = 2.0 * M * n_local * K
+    achieved = gemm_flops / (gemm_ms / 1e3) / 1e12
+    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        with open(tpath) as f:
+            tj = json.load(f)
+        per_tile_pair = tj.get("fp8_gemm_dram_bytes_per_flop")
+        if per_tile_pair is not None:
+            traffic = per_tile_pair * gemm_flops
+    roofline = {"kernel": "fp8_gemm_kernel<BLOCK_N=256>", "bound": "tensor", "achieved": achieved, "peak": fp8_peak,
+                "unit": "TFLOP/s", "frac": achieved / fp8_peak, "traffic": traffic,
+                "peak_source": f"2 x {peaks['source']} bf16 burst {peaks['bf16_tflops']} TFLOP/s "
+                               "(e4m3 tensor rate is twice bf16; no FP8 figure is measured on this pool)",
+                "frac_of_2x_sustained_bf16": achieved / (2.0 * peaks["bf16_tflops_sustained"]),
+                "frac_of_nominal_4.5PF": achieved / 4500.0,
+                "algorithmic_flops_per_launch": gemm_flops, "avg_launch_ms": gemm_ms,
+                "quant_kernel": {"bound": "hbm", "achieved": (3.0 * M * K + 4 * M * (K // 128)) / (quant_ms / 1e3) / 1e9,
+                                 "peak": peaks["hbm_gbs"], "unit": "GB/s", "avg_launch_ms": quant_ms}}
+    roofline["quant_kernel"]["frac"] = roofline["quant_kernel"]["achieved"] / peaks["hbm_gbs"]
+
+    line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "e4m3 (fp32 accumulate, bf16 out)", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "M": M, "N": N, "K": K, "n_per_gpu": n_local,
+                       "step": "per_token_cast_to_fp8(A) + gemm_fp8_fp8_bf16_nt", "parallelism": f"n-split x{world}",
+                       "l2": "per-step operands (A8 67 MB + B8 shard + D shard) exceed the 126 MB L2", "device": dev_name},
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": a_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
+                    "note": "weights stay resident on the device; activations in, outputs out through pinned memory"},
+            "gpu_launches": 2 * args.steps, "clocks": clocks, "roofline": roofline}
+
+    del a_host, out_host, a_dev, out, lhs, rhs, a
+    torch.cuda.empty_cache()
+
+    if rank == 0 and world == 1 and not args.no_extras:
+        extras = []
+        for m_small in (16, 64):
+            extras.append(bench_decode(m_small, peaks))
+        extras.append(bench_dense("C3 mid-size projection", 4096, 7168, 18432, peaks))
+        extras.append(bench_dense("C1 CPU-runnable", 256, 1024, 1024, peaks))
+        line["other_workloads"] = extras
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        a_cpu, rhs_cpu = make_cpu_inputs()
+        cpu_reference_step(a_cpu, rhs_cpu)
+        reps, t0 = 0, time.perf_counter()
+        while reps < 3 or (time.perf_counter() - t0 < 10.0 and reps < 50):
+            cpu_reference_step(a_cpu, rhs_cpu)
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        line["cpu_baseline"] = {"value": 2.0 * CPU_SLAB_ROWS * N * K / dt / 1e12, "unit": "TFLOP/s",
+                                "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": f"{reps} passes over a {CPU_SLAB_ROWS}-row slab of A against the full B "
+                                          f"(quantize, dequantize both operands, fp32 torch.matmul, bf16)"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_case(args) -> None:
+    """One shape, `steps` launches after `warmup`: the small workload that profiler captures are taken on."""
+    import yan_b200
+    dims = [int(v) for v in args.case.split(",")]
+    m, n, k = dims[:3]
+    block_n = dims[3] if len(dims) > 3 else 0
+    torch.cuda.set_device(0)
+    a, rhs = make_device_inputs(m, n, k, 0, outliers=(m <= 64))
+    lhs = yan_b200.per_token_cast_to_fp8(a)
+    out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    for _ in range(args.warmup):
+        yan_b200.per_token_cast_to_fp8(a, out=lhs)
+        yan_b200.gemm_fp8_fp8_bf16_nt(lhs, rhs, out, block_n=block_n)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        yan_b200.per_token_cast_to_fp8(a, out=lhs)
+        yan_b200.gemm_fp8_fp8_bf16_nt(lhs, rhs, out, block_n=block_n)
+    e1.record()
+    torch.cuda.synchronize()
+    assert yan_b200.read_device_status() == 0
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({"case": [m, n, k], "block_n": block_n, "ms_per_step": ms,
+                      "TFLOP/s": 2.0 * m * n * k / (ms / 1e3) / 1e12}), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the decode / C3 / C1 side measurements")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--case", default=None, metavar="M,N,K[,BLOCK_N]",
+                    help="profiling aid: run quantize + GEMM of one shape `--steps` times on one GPU and print its timing")
+    args = ap.parse_args()
+    if args.case is not None:
+        return run_case(args)
+    assert args.warmup >= 3 or args.impl == "reference", "at least 3 warm-up steps"
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

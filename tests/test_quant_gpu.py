@@ -34,7 +34,7 @@ def test_per_token_cast_edge_values(cuda_lib):
     """all-zero groups (amax floor), tiny and huge magnitudes, exact ties, negative zero."""
     x = torch.zeros(8, 512, dtype=torch.float32)
     x[1, :128] = 1e-6
-    x[2, 128:256] = torch.linspace(-3e38, 3e38, 128)
+    x[2, 128:256] = torch.linspace(-1.5e38, 1.5e38, 128)  # finite: NaN/Inf inputs are outside the contract
     x[3] = torch.arange(512, dtype=torch.float32) - 256.0
     x[4, ::2] = -0.0
     x[5] = torch.tensor([17.0, 19.0, 448.0, 464.0] * 128)
