@@ -13,7 +13,8 @@ import os
 from typing import Optional
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG_DIR, "lib", "libyan_b200.so")
+# YAN_B200_LIBRARY points at an alternative build of the same ABI (e.g. one compiled with other flags).
+LIB_PATH = os.environ.get("YAN_B200_LIBRARY") or os.path.join(_PKG_DIR, "lib", "libyan_b200.so")
 
 _P = ctypes.c_void_p
 _I = ctypes.c_int

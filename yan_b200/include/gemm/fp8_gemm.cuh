@@ -123,15 +123,24 @@ struct GemmSmemLayout {
 };
 
 template <uint32_t BLOCK_N, uint32_t kNumStages, GemmType kGemmType, typename out_t>
-__global__ void __launch_bounds__(get_num_threads_per_sm<>(kBlockM), 1)
+__global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     fp8_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tensor_map_a,
                     const __grid_constant__ CUtensorMap tensor_map_b) {
 #if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ >= 1000)
     using L = GemmSmemLayout<BLOCK_N, kNumStages>;
     using Sched = Scheduler<kGemmType, kBlockM, BLOCK_N>;
     constexpr uint32_t kNumTmemBufs = L::kNumTmemBufs;
-    constexpr uint32_t kColsPerWG = BLOCK_N / 2;
-    constexpr uint32_t kNumMathWarps = 8;
+    constexpr uint32_t kNumMathWGs = get_num_math_warpgroups(BLOCK_N);
+    static_assert(RegisterBudgetCheck<BLOCK_N>::ok);
+    constexpr uint32_t kColsPerWG = BLOCK_N / kNumMathWGs;
+    constexpr uint32_t kNumMathWarps = 4 * kNumMathWGs;
+    constexpr uint32_t kMaxChunk = (kNumMathWGs == 4) ? 16 : 32;             // 112 registers leave room for 16
+    constexpr uint32_t kChunk = kColsPerWG < kMaxChunk ? kColsPerWG : kMaxChunk;  // columns per tcgen05.ld
+    constexpr uint32_t kNumChunks = kColsPerWG / kChunk;
+    // With 4 warpgroups the other warps of the sub-partition hide a warp's TMEM-load latency and the
+    // register budget (120) has no room for a second landing buffer; with 2 the loads are double-buffered.
+    constexpr bool kDoubleBuffer = (kNumMathWGs == 2) && (kNumChunks > 1);
+    constexpr uint32_t kScaleDepth = (kNumMathWGs == 4) ? 2 : 4;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -177,7 +186,7 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(kBlockM), 1)
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp_idx < 4) {
-        ptx::reg_dealloc<kNumControlRegisters>();
+        ptx::reg_dealloc<get_num_control_registers(BLOCK_N)>();
 
         if (warp_idx == 0 && lane_idx == 0) {
             // ------------------------------ TMA producer ------------------------------
@@ -250,7 +259,7 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(kBlockM), 1)
         __syncwarp();
     } else {
         // ------------------------------ promotion + epilogue warpgroups ------------------------------
-        ptx::reg_alloc<kNumMathRegisters>();
+        ptx::reg_alloc<get_num_math_registers(BLOCK_N)>();
 
         const uint32_t wg = (warp_idx - 4) / 4;
         const uint32_t quarter = warp_idx % 4;
@@ -273,56 +282,76 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(kBlockM), 1)
             const float* sa_ptr = p.scales_a + row;
             const float* sb_ptr = p.scales_b + (static_cast<size_t>(group) * num_sb_rows + sb_row) * num_k_blocks;
 
-            float sa_next = row_ok ? __ldg(sa_ptr) : 0.0f;
-            float sb_next = __ldg(sb_ptr);
-            for (uint32_t kb = 0; kb < num_k_blocks; ++kb) {
-                const float scale = sa_next * sb_next;
-                if (kb + 1 < num_k_blocks) {
-                    sa_next = row_ok ? __ldg(sa_ptr + static_cast<size_t>(kb + 1) * p.sa_ld) : 0.0f;
-                    sb_next = __ldg(sb_ptr + kb + 1);
-                }
-                const bool ok = detail::bounded_wait(tmem_full_barriers + buf, buf_phase, abort_flag, p, 4);
-                if (!__all_sync(0xffffffffu, ok)) {
-                    alive = false;
-                    break;
-                }
-                ptx::tcgen05_fence_after_thread_sync();
-                const uint32_t taddr = tmem_lane_base + buf * BLOCK_N;
-                if constexpr (kColsPerWG % 64 == 0) {
+            // Scales are prefetched kScaleDepth k-blocks ahead: one L2 round trip is longer than one k-block.
+            float sa_ring[kScaleDepth], sb_ring[kScaleDepth];
 #pragma unroll
-                    for (uint32_t c = 0; c < kColsPerWG / 64; ++c) {
-                        uint32_t r[64];
-                        ptx::tmem_ld_32x32b_x64_wait(taddr + c * 64, r);
-                        if (kb == 0) {
+            for (uint32_t i = 0; i < kScaleDepth; ++i) {
+                sa_ring[i] = (row_ok && i < num_k_blocks) ? __ldg(sa_ptr + static_cast<size_t>(i) * p.sa_ld) : 0.0f;
+                sb_ring[i] = (i < num_k_blocks) ? __ldg(sb_ptr + i) : 0.0f;
+            }
 #pragma unroll
-                            for (uint32_t j = 0; j < 64; ++j) acc[c * 64 + j] = scale * __uint_as_float(r[j]);
-                        } else {
+            for (uint32_t j = 0; j < kColsPerWG; ++j) acc[j] = 0.0f;
+
+            for (uint32_t kb0 = 0; kb0 < num_k_blocks && alive; kb0 += kScaleDepth) {
 #pragma unroll
-                            for (uint32_t j = 0; j < 64; ++j)
-                                acc[c * 64 + j] = fmaf(scale, __uint_as_float(r[j]), acc[c * 64 + j]);
+                for (uint32_t i = 0; i < kScaleDepth; ++i) {
+                    const uint32_t kb = kb0 + i;
+                    if (!alive || kb >= num_k_blocks) continue;
+                    const float scale = sa_ring[i] * sb_ring[i];
+                    if (kb + kScaleDepth < num_k_blocks) {
+                        sa_ring[i] = row_ok ? __ldg(sa_ptr + static_cast<size_t>(kb + kScaleDepth) * p.sa_ld) : 0.0f;
+                        sb_ring[i] = __ldg(sb_ptr + kb + kScaleDepth);
+                    }
+                    const bool ok = detail::bounded_wait(tmem_full_barriers + buf, buf_phase, abort_flag, p, 4);
+                    if (!__all_sync(0xffffffffu, ok)) {
+                        alive = false;
+                        continue;
+                    }
+                    ptx::tcgen05_fence_after_thread_sync();
+                    const uint32_t taddr = tmem_lane_base + buf * BLOCK_N;
+
+                    // Chunks of kChunk columns move TMEM -> registers.  The TMEM buffer is handed back as soon
+                    // as the last chunk has landed, before its FMAs.
+                    if constexpr (kDoubleBuffer) {
+                        uint32_t t0[kChunk], t1[kChunk];
+                        ptx::tmem_ld_32x32b<kChunk>(taddr, t0);
+                        ptx::tmem_ld_wait<kChunk>(t0);
+#pragma unroll
+                        for (uint32_t c = 0; c < kNumChunks; ++c) {
+                            uint32_t(&cur)[kChunk] = (c & 1) ? t1 : t0;
+                            uint32_t(&nxt)[kChunk] = (c & 1) ? t0 : t1;
+                            if (c + 1 < kNumChunks) {
+                                ptx::tmem_ld_32x32b<kChunk>(taddr + (c + 1) * kChunk, nxt);
+                            } else {
+                                ptx::tcgen05_fence_before_thread_sync();
+                                __syncwarp();
+                                if (lane_idx == 0) ptx::mbar_arrive(tmem_empty_barriers + buf);
+                            }
+#pragma unroll
+                            for (uint32_t j = 0; j < kChunk; ++j)
+                                acc[c * kChunk + j] = fmaf(scale, __uint_as_float(cur[j]), acc[c * kChunk + j]);
+                            if (c + 1 < kNumChunks) ptx::tmem_ld_wait<kChunk>(nxt);
+                        }
+                    } else {
+#pragma unroll
+                        for (uint32_t c = 0; c < kNumChunks; ++c) {
+                            uint32_t t[kChunk];
+                            ptx::tmem_ld_32x32b<kChunk>(taddr + c * kChunk, t);
+                            ptx::tmem_ld_wait<kChunk>(t);
+                            if (c + 1 == kNumChunks) {
+                                ptx::tcgen05_fence_before_thread_sync();
+                                __syncwarp();
+                                if (lane_idx == 0) ptx::mbar_arrive(tmem_empty_barriers + buf);
+                            }
+#pragma unroll
+                            for (uint32_t j = 0; j < kChunk; ++j)
+                                acc[c * kChunk + j] = fmaf(scale, __uint_as_float(t[j]), acc[c * kChunk + j]);
                         }
                     }
-                } else if constexpr (kColsPerWG == 32) {
-                    uint32_t r[32];
-                    ptx::tmem_ld_32x32b_x32_wait(taddr, r);
-#pragma unroll
-                    for (uint32_t j = 0; j < 32; ++j)
-                        acc[j] = (kb == 0) ? scale * __uint_as_float(r[j]) : fmaf(scale, __uint_as_float(r[j]), acc[j]);
-                } else {
-                    static_assert(kColsPerWG == 16 || kColsPerWG % 64 == 0 || kColsPerWG == 32, "unsupported BLOCK_N");
-                    uint32_t r[16];
-                    ptx::tmem_ld_32x32b_x16_wait(taddr, r);
-#pragma unroll
-                    for (uint32_t j = 0; j < 16; ++j)
-                        acc[j] = (kb == 0) ? scale * __uint_as_float(r[j]) : fmaf(scale, __uint_as_float(r[j]), acc[j]);
-                }
-                // All of this warp's TMEM reads of the buffer are complete: hand it back to the MMA thread.
-                ptx::tcgen05_fence_before_thread_sync();
-                __syncwarp();
-                if (lane_idx == 0) ptx::mbar_arrive(tmem_empty_barriers + buf);
-                if (++buf == kNumTmemBufs) {
-                    buf = 0;
-                    buf_phase ^= 1;
+                    if (++buf == kNumTmemBufs) {
+                        buf = 0;
+                        buf_phase ^= 1;
+                    }
                 }
             }
             if (alive && row_ok) {
@@ -426,7 +455,7 @@ struct GemmLauncher {
             const uint32_t tiles = ceil_div(a.m, kBlockM) * ceil_div(a.n, BLOCK_N);
             grid = tiles < grid ? tiles : grid;
         }
-        kernel<<<grid, get_num_threads_per_sm<>(kBlockM), kSmemSize, stream>>>(p, map_a, map_b);
+        kernel<<<grid, get_num_threads_per_sm<>(BLOCK_N), kSmemSize, stream>>>(p, map_a, map_b);
         return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
     }
 };

@@ -16,22 +16,47 @@ namespace yan {
 // warp 1      : MMA issuer   (one elected lane)
 // warp 2      : TMEM allocator / deallocator
 // warp 3      : spare (keeps the first four warps a full warpgroup for setmaxnreg)
-// warps 4..11 : two promotion/epilogue warpgroups; warpgroup h owns output columns
-//               [h*BLOCK_N/2, (h+1)*BLOCK_N/2) of the tile, warp (w%4) owns TMEM lanes 32*(w%4)..+31.
+// warps 4..   : promotion/epilogue warpgroups; warpgroup h owns output columns
+//               [h*BLOCK_N/G, (h+1)*BLOCK_N/G) of the tile, warp (w%4) owns TMEM lanes 32*(w%4)..+31.
+// G = 2 everywhere.  G = 4 (sixteen promotion warps, 64 columns each, 112 registers) was measured slower
+// for BLOCK_N = 256: all promotion warps are released by the same barrier, so they load in lockstep and
+// then issue FMAs in lockstep, and extra warps add contention instead of overlap.
 constexpr uint32_t kNumControlThreads = 128;
 constexpr uint32_t kNumMathThreadsPerGroup = 128;
 
-__host__ __device__ constexpr int get_num_math_warpgroups(int /*block_m*/) { return 2; }
+__host__ __device__ constexpr uint32_t get_num_math_warpgroups(uint32_t /*block_n*/) { return 2; }
 
 template <uint32_t kNumTMAThreads = kNumControlThreads, uint32_t kNumMathThreads = kNumMathThreadsPerGroup>
-__host__ __device__ constexpr int get_num_threads_per_sm(int block_m) {
+__host__ __device__ constexpr uint32_t get_num_threads_per_sm(uint32_t block_n) {
     static_assert(kNumMathThreads == 128, "a promotion warpgroup is 128 threads (4 TMEM lane quarters)");
-    return get_num_math_warpgroups(block_m) * kNumMathThreads + kNumTMAThreads;
+    return get_num_math_warpgroups(block_n) * kNumMathThreads + kNumTMAThreads;
 }
 
-// Registers after setmaxnreg: 128*40 + 256*232 = 64512 <= 65536 (same split as fp8_gemm.cuh:171-172).
-constexpr uint32_t kNumControlRegisters = 40;
-constexpr uint32_t kNumMathRegisters = 232;
+// Registers after setmaxnreg (the mechanism of fp8_gemm.cuh:171-181 in the reference).  The pool that
+// setmaxnreg.inc draws from is what the CTA was given at launch (registers per thread at launch x threads),
+// NOT the whole register file: an increase that the control warpgroup's decrease does not cover blocks
+// forever.  Launch allocation = floor(65536 / threads / 8) * 8 registers per thread.
+//   2 math warpgroups: launch 168 x 384; 128*40 + 256*232 = 64512 = 168*384
+//   4 math warpgroups: launch  96 x 640; 128*32 + 512*112 = 61440 =  96*640
+__host__ __device__ constexpr uint32_t get_num_launch_registers(uint32_t block_n) {
+    return (65536u / get_num_threads_per_sm<>(block_n)) / 8u * 8u;
+}
+__host__ __device__ constexpr uint32_t get_num_control_registers(uint32_t block_n) {
+    return get_num_math_warpgroups(block_n) == 4 ? 32 : 40;
+}
+__host__ __device__ constexpr uint32_t get_num_math_registers(uint32_t block_n) {
+    return get_num_math_warpgroups(block_n) == 4 ? 112 : 232;
+}
+
+template <uint32_t BLOCK_N>
+struct RegisterBudgetCheck {
+    static constexpr uint32_t launch = get_num_launch_registers(BLOCK_N);
+    static constexpr uint32_t freed = kNumControlThreads * (launch - get_num_control_registers(BLOCK_N));
+    static constexpr uint32_t wanted =
+        get_num_math_warpgroups(BLOCK_N) * kNumMathThreadsPerGroup * (get_num_math_registers(BLOCK_N) - launch);
+    static_assert(wanted <= freed, "setmaxnreg.inc would wait forever: the decrease does not cover the increase");
+    static constexpr bool ok = true;
+};
 
 // --- instruction descriptor (32 bit) for tcgen05.mma kind::f8f6f4 ------------------------------
 //  [4,6)  accumulator format: 1 = fp32
