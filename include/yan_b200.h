@@ -107,6 +107,31 @@ void yan_b200_fp8_linear_bf16(const void* a, const void* rhs, const void* rhs_sc
                               int block_n, int* return_code);
 
 /*
+ * Quantize-then-GEMM for callers that must not allocate.  No counterpart in the reference.
+ *
+ * Some hosts of this library cannot call cudaMalloc or let a framework allocator do it for them: a
+ * serving loop that has handed all of its device memory to a KV-cache pool, a plugin running inside
+ * another runtime's memory budget, code on a latency path where an allocation may synchronise the
+ * device.  For them this variant of yan_b200_fp8_linear_bf16 keeps the intermediate (quantized
+ * activations and their scales) in a fixed array inside the library's device image instead of a
+ * caller-provided workspace.  Inputs and the output are still the caller's.
+ *
+ *   - Limit: m * k <= YAN_B200_STATIC_SCRATCH_MAX_ELEMENTS (8 Mi elements; 8.25 MiB of device memory
+ *     per GPU that loads the library, held until the process exits).  Larger problems return
+ *     YAN_B200_WORKSPACE_TOO_SMALL; use yan_b200_fp8_linear_bf16 with your own workspace instead.
+ *   - The first call on each device looks up the array's device address (one cudaGetSymbolAddress, made
+ *     with that device current).  Make that first call before any stream capture begins.
+ *   - The call allocates and frees nothing and calls no allocating library routine.
+ *   - All calls on a device share the one array, which keeps whatever the last call left there.  Nothing
+ *     in it needs to start at zero (the quantizer rewrites every byte the GEMM reads), but two calls
+ *     that overlap on the GPU -- different streams, or graphs replayed concurrently -- race on it.
+ *     Order them on one stream or with events.
+ */
+#define YAN_B200_STATIC_SCRATCH_MAX_ELEMENTS (8u << 20)
+void yan_b200_fp8_linear_bf16_static(const void* a, const void* rhs, const void* rhs_scales, void* out, int m, int n,
+                                     int k, int ldd, void* stream, int num_sms, int block_n, int* return_code);
+
+/*
  * Device status word of the current device: 0, or (YAN_B200_DEVICE_TIMEOUT << 8) | site when a bounded
  * device-side wait of the GEMM ran out.  Synchronises the device.  reset != 0 clears the word.
  * Plays the role of the reference's error conventions (yan/jit/template.py:134 return code;

@@ -32,9 +32,13 @@ SIGNATURES = {
     "yan_b200_per_block_cast_to_fp8": (None, [_P, _P, _P, _I, _I, _P, _RC]),
     "yan_b200_fp8_linear_workspace_bytes": (ctypes.c_size_t, [_I, _I]),
     "yan_b200_fp8_linear_bf16": (None, [_P, _P, _P, _P, _P, ctypes.c_size_t, _I, _I, _I, _I, _P, _I, _I, _RC]),
+    "yan_b200_fp8_linear_bf16_static": (None, [_P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _RC]),
     "yan_b200_read_device_status": (None, [_RC, _I, _RC]),
     "yan_b200_set_wait_timeout_ns": (None, [ctypes.c_ulonglong]),
 }
+
+# YAN_B200_STATIC_SCRATCH_MAX_ELEMENTS of include/yan_b200.h
+STATIC_SCRATCH_MAX_ELEMENTS = 8 << 20
 
 _lib: Optional[ctypes.CDLL] = None
 

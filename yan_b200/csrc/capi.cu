@@ -33,6 +33,30 @@ int* status_word_of_current_device() {
     return g_status_ptr[dev];
 }
 
+// Scratch of the allocation-free entry point: quantized activations followed by their scales.
+// Every device that loads this library holds these bytes until the process exits.
+constexpr size_t kStaticScratchQBytes = YAN_B200_STATIC_SCRATCH_MAX_ELEMENTS;  // one byte per element
+constexpr size_t kStaticScratchScaleBytes = kStaticScratchQBytes / 128 * sizeof(float);
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchQBytes + kStaticScratchScaleBytes];
+
+unsigned char* g_static_scratch_ptr[kMaxDevices] = {};
+
+// In host code `g_static_scratch` is only a handle; the device address has to be asked for, once per
+// device, with that device current.
+unsigned char* static_scratch_of_current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        unsigned char* p = nullptr;
+        if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_scratch) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        g_static_scratch_ptr[dev] = p;
+    }
+    return g_static_scratch_ptr[dev];
+}
+
 inline void set_rc(int* rc, int v) {
     if (rc != nullptr) *rc = v;
 }
@@ -208,6 +232,22 @@ YAN_EXPORT void yan_b200_fp8_linear_bf16(const void* a, const void* rhs, const v
     uint8_t* q = static_cast<uint8_t*>(workspace);
     float* scales = reinterpret_cast<float*>(q + yan::align_up(static_cast<size_t>(m) * k, static_cast<size_t>(256)));
     int rc = yan::launch_per_token_cast_to_fp8(a, q, scales, m, k, k, m, static_cast<cudaStream_t>(stream));
+    if (rc != yan::kOk) return set_rc(return_code, rc);
+    yan_b200_gemm_fp8_fp8_bf16_nt(q, scales, rhs, rhs_scales, out, m, n, k, ldd, stream, num_sms, block_n, return_code);
+}
+
+YAN_EXPORT void yan_b200_fp8_linear_bf16_static(const void* a, const void* rhs, const void* rhs_scales, void* out,
+                                                int m, int n, int k, int ldd, void* stream, int num_sms, int block_n,
+                                                int* return_code) {
+    if (!positive(m, n, k) || k % 128 != 0) return set_rc(return_code, yan::kBadArgument);
+    const size_t elements = static_cast<size_t>(m) * static_cast<size_t>(k);
+    if (elements > kStaticScratchQBytes || elements / 128 * sizeof(float) > kStaticScratchScaleBytes)
+        return set_rc(return_code, yan::kWorkspaceTooSmall);  // M * K exceeds the built-in scratch
+    unsigned char* scratch = static_scratch_of_current_device();
+    if (scratch == nullptr) return set_rc(return_code, yan::kLaunchFailed);
+    uint8_t* q = scratch;
+    float* scales = reinterpret_cast<float*>(scratch + kStaticScratchQBytes);
+    const int rc = yan::launch_per_token_cast_to_fp8(a, q, scales, m, k, k, m, static_cast<cudaStream_t>(stream));
     if (rc != yan::kOk) return set_rc(return_code, rc);
     yan_b200_gemm_fp8_fp8_bf16_nt(q, scales, rhs, rhs_scales, out, m, n, k, ldd, stream, num_sms, block_n, return_code);
 }
