@@ -1,0 +1,125 @@
+"""Host-side logic of the sharded GEMMs on CPU ranks (gloo, world size 2): shard slicing, reassembly and the
+allreduce of partials.  The arithmetic is substituted by the CPU oracle through `gemm_fn`; the CUDA kernels are
+covered by the GPU tests."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _oracle_gemm(lhs, rhs, out):
+    from oracle import ref
+    qa, sa = lhs
+    d = ref.ref_gemm_f32((qa.contiguous(), sa.contiguous()), (rhs[0].contiguous(), rhs[1].contiguous()))
+    out.copy_(d.to(out.dtype))
+
+
+def _worker(rank: int, world: int, port: int, mode: str, results):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import ref
+        from yan_b200.comm import gemm_allreduce as ga
+        torch.set_num_threads(2)
+        m, n, k = 160, 512, 1024
+        a, b = ref.make_inputs(m, n, k, seed=3)
+        lhs, rhs = ref.per_token_cast_to_fp8(a), ref.per_block_cast_to_fp8(b)
+        d_ref = ref.ref_gemm(lhs, rhs)
+        if mode == "n_split":
+            full = torch.zeros(m, n, dtype=torch.bfloat16)
+            ga.gemm_n_split(lhs, ga.shard_n(rhs, rank, world), full, rank, world, gemm_fn=_oracle_gemm)
+            ns = n // world
+            assert bool((full[:, :rank * ns] == 0).all()) and bool((full[:, (rank + 1) * ns:] == 0).all())
+            dist.all_reduce(full_f := full.float())                     # test-only reassembly of the column slices
+            ok = ref.rel_frobenius(full_f.to(torch.bfloat16), d_ref) <= 1e-3
+            own = torch.empty(m, ns, dtype=torch.bfloat16)
+            ga.gemm_n_split(lhs, ga.shard_n(rhs, rank, world), own, rank, world, gemm_fn=_oracle_gemm)
+            ok = ok and torch.equal(own, full[:, rank * ns:(rank + 1) * ns])
+        elif mode == "k_split_f32":
+            # quantize the local K shard of A: equals the shard of the quantized A
+            ks = k // world
+            lhs_local = ref.per_token_cast_to_fp8(a[:, rank * ks:(rank + 1) * ks].contiguous())
+            sh = ga.shard_k(lhs, rank, world)
+            assert torch.equal(lhs_local[0].view(torch.uint8), sh[0].view(torch.uint8)) and torch.equal(lhs_local[1], sh[1])
+            out = torch.empty(m, n, dtype=torch.bfloat16)
+            ga.gemm_k_split_allreduce(lhs_local, ga.shard_k(rhs, rank, world), out, partial_dtype=torch.float32,
+                                      num_chunks=2, gemm_fn=_oracle_gemm)
+            ok = ref.rel_frobenius(out, d_ref) <= 1e-3
+        elif mode == "k_split_bf16":
+            out = torch.empty(m, n, dtype=torch.bfloat16)
+            ga.gemm_k_split_allreduce(ga.shard_k(lhs, rank, world), ga.shard_k(rhs, rank, world), out,
+                                      partial_dtype=torch.bfloat16, gemm_fn=_oracle_gemm)
+            d_split = ref.ref_gemm_k_split(lhs, rhs, world)
+            ok = ref.rel_frobenius(out, d_split) <= 2e-3 and ref.rel_frobenius(out, d_ref) <= 6e-3
+        elif mode == "rank_failure":
+            # A rank that raises before the collective: the survivor's allreduce must end with an error, not hang.
+            if rank == 1:
+                raise RuntimeError("injected host-side failure before the allreduce")
+            out = torch.empty(m, n, dtype=torch.bfloat16)
+            try:
+                ga.gemm_k_split_allreduce(ga.shard_k(lhs, rank, world), ga.shard_k(rhs, rank, world), out,
+                                          partial_dtype=torch.float32, gemm_fn=_oracle_gemm)
+                ok = False
+            except Exception:
+                ok = True
+        else:
+            ok = False
+        results[rank] = bool(ok)
+    finally:
+        if mode != "rank_failure":
+            dist.destroy_process_group()
+
+
+def _run(mode: str, expect_all: bool = True):
+    world = 2
+    ctx = mp.get_context("spawn")
+    results = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, mode, results)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+        if p.is_alive():
+            p.terminate()
+            pytest.fail(f"{mode}: rank did not finish")
+    return dict(results), [p.exitcode for p in procs]
+
+
+@pytest.mark.parametrize("mode", ["n_split", "k_split_f32", "k_split_bf16"])
+def test_sharded_gemm_world2_gloo(mode):
+    results, codes = _run(mode)
+    assert codes == [0, 0], codes
+    assert results == {0: True, 1: True}, results
+
+
+def test_rank_failure_surfaces_as_error_not_hang():
+    results, codes = _run("rank_failure")
+    assert codes[1] != 0                    # the failing rank exits with its exception
+    assert results.get(0) is True           # the survivor saw an error from the collective
+
+
+def test_shard_helpers_reject_ragged_cuts():
+    from yan_b200.comm import gemm_allreduce as ga
+    q = torch.zeros(384, 256, dtype=torch.uint8)
+    s = torch.zeros(3, 2)
+    with pytest.raises(AssertionError):
+        ga.shard_n((q, s), 0, 2)            # 384 / 2 = 192 rows: not whole 128-row blocks
+    with pytest.raises(AssertionError):
+        ga.shard_k((q, s), 0, 4)            # 256 / 4 = 64 columns: not whole k-blocks
+    qs, ss = ga.shard_k((q, s), 1, 2)
+    assert qs.shape == (384, 128) and ss.shape == (3, 1)

@@ -1,0 +1,76 @@
+"""Sharded GEMMs on real GPUs over NCCL (needs at least two visible devices; skipped on a one-GPU box)."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, results):
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import yan_b200
+        from oracle import ref
+        from yan_b200.comm import gemm_allreduce as ga
+        m, n, k = 512, 1024, 2048
+        a, b = ref.make_inputs(m, n, k, seed=3)
+        lhs, rhs = ref.per_token_cast_to_fp8(a), ref.per_block_cast_to_fp8(b)
+        d_ref = ref.ref_gemm(lhs, rhs)
+        cm = lambda op: (op[0].contiguous().cuda(), op[1].t().contiguous().cuda().t())
+        rm = lambda op: (op[0].contiguous().cuda(), op[1].contiguous().cuda())
+        ok = True
+        # N-split into the full buffer, then gather the slices for the check only
+        full = torch.zeros(m, n, dtype=torch.bfloat16, device="cuda")
+        ga.gemm_n_split(cm(lhs), rm(ga.shard_n(rhs, rank, world)), full, rank, world)
+        dist.all_reduce(full)
+        ok &= ref.rel_frobenius(full.cpu(), d_ref) <= 1e-3
+        # K-split: local quantization of the A shard, bf16 partials and fp32 partials, chunked
+        ks = k // world
+        lhs_local = yan_b200.per_token_cast_to_fp8(a[:, rank * ks:(rank + 1) * ks].contiguous().cuda())
+        rhs_k = rm(ga.shard_k(rhs, rank, world))
+        out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+        ga.gemm_k_split_allreduce(lhs_local, rhs_k, out, partial_dtype=torch.bfloat16, num_chunks=2)
+        torch.cuda.synchronize()
+        ok &= ref.rel_frobenius(out.cpu(), ref.ref_gemm_k_split(lhs, rhs, world)) <= 2e-3
+        ga.gemm_k_split_allreduce(lhs_local, rhs_k, out, partial_dtype=torch.float32, num_chunks=4)
+        torch.cuda.synchronize()
+        ok &= ref.rel_frobenius(out.cpu(), d_ref) <= 1e-3
+        ok &= yan_b200.read_device_status() == 0
+        results[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_n_split_and_k_split_over_nccl(cuda_lib):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    ctx = mp.get_context("spawn")
+    results = ctx.Manager().dict()
+    port = _free_port()
+    env = dict(NCCL_NVLS_ENABLE="0")
+    os.environ.update(env)
+    procs = [ctx.Process(target=_worker, args=(r, world, port, results)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(240)
+        assert not p.is_alive(), "rank did not finish"
+    assert [p.exitcode for p in procs] == [0, 0]
+    assert dict(results) == {0: True, 1: True}
