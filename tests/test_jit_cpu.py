@@ -49,7 +49,7 @@ def test_type_maps_cover_the_reference_types():
 
 def test_fp8_gemm_template_keeps_the_reference_variable_names():
     from yan_b200.jit_kernels import gemm
-    for token in ("{N}", "{K}", "{BLOCK_M}", "{BLOCK_N}", "{NUM_STAGES}", "{NUM_TMA_MULTICAST}", "make_2d_tma_a_desc(lhs, m)",
+    for token in ("{N}", "{K}", "{BLOCK_M}", "{BLOCK_N}", "{NUM_STAGES}", "make_2d_tma_a_desc(lhs, m)",
                   "make_2d_tma_b_desc(rhs)", "make_2d_tma_scales_a_desc(lhs_scales, m)", "make_2d_tma_d_desc(out, m)",
                   "GemmType::run(out, rhs_scales, nullptr", "stream, num_sms, smem_size"):
         assert token in gemm.template
@@ -90,7 +90,7 @@ def test_fp8_gemm_template_cross_compiles(tmp_path, monkeypatch):
     monkeypatch.setenv("YAN_CACHE_DIR", str(tmp_path))
     compiler.get_default_user_dir.cache_clear()
     try:
-        keys = {'N': 1024, 'K': 1024, 'BLOCK_M': 128, 'BLOCK_N': 64, 'NUM_STAGES': 8, 'NUM_TMA_MULTICAST': 1}
+        keys = {'N': 1024, 'K': 1024, 'BLOCK_M': 128, 'BLOCK_N': 64, 'NUM_STAGES': 8}
         code = jit.generate(gemm.includes, gemm.arg_defs, jit.cpp_format(gemm.template, keys))
         rt = jit.build("gemm_fp8_fp8_bf16_nt", gemm.arg_defs, code)
         assert os.path.exists(os.path.join(rt.path, "kernel.so"))

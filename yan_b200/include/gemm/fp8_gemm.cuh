@@ -463,8 +463,8 @@ struct GemmLauncher {
 // ---------------------------------------------------------------------------------------------
 // `Gemm<...>`: the host class the reference's launch template instantiates but never defines
 // (yan/jit_kernels/gemm.py:20-30).  Template parameter order and the member names are the
-// template's; kNumTMAMulticast is accepted for source compatibility and must be 1 (this kernel
-// never multicasts).  The scale and output "descriptors" carry plain pointers because the kernel
+// template's; the eighth parameter (the reference's TMA multicast width) is accepted for source
+// compatibility and must be 1: this kernel never multicasts.  The scale and output "descriptors" carry plain pointers because the kernel
 // reads scales with ordinary loads and writes D with 16-byte stores.
 // ---------------------------------------------------------------------------------------------
 struct ScalesADesc {
@@ -477,10 +477,10 @@ struct OutDesc {
 };
 
 template <uint32_t SHAPE_N, uint32_t SHAPE_K, uint32_t BLOCK_M, uint32_t BLOCK_N, uint32_t BLOCK_K, uint32_t kNumGroups,
-          uint32_t kNumStages, uint32_t kNumTMAMulticast, GemmType kGemmType>
+          uint32_t kNumStages, uint32_t kNumCtasPerLoad, GemmType kGemmType>
 class Gemm {
     static_assert(BLOCK_M == kBlockM && BLOCK_K == kBlockK, "this kernel is built around 128 x BLOCK_N x 128 tiles");
-    static_assert(kNumTMAMulticast == 1, "cluster multicast is not used by this kernel");
+    static_assert(kNumCtasPerLoad == 1, "every CTA loads its own tiles: the load width must be 1");
     static_assert(SHAPE_K % BLOCK_K == 0, "K must be a multiple of 128");
 
 public:

@@ -2,7 +2,8 @@
 
 yan/jit_kernels/gemm.py:1-31 consists of a launch template only.  This module keeps that template
 (same variable names: lhs, lhs_scales, rhs, rhs_scales, out, m, stream, num_sms, smem_size; same
-JIT keys N, K, BLOCK_M, BLOCK_N, NUM_STAGES, NUM_TMA_MULTICAST) and adds the missing functions.
+JIT keys N, K, BLOCK_M, BLOCK_N, NUM_STAGES) and adds the missing functions.  The reference's sixth key, the number
+of CTAs one TMA load is delivered to, is fixed at 1: every CTA of this kernel loads its own tiles.
 By default a call goes to the prebuilt C-ABI library; `YAN_FP8_GEMM_JIT=1` routes it through
 `jit_tuner.compile_and_tune` with the template below, specialising N and K at compile time exactly
 as the reference intends.  Both run the same kernel source (include/gemm/fp8_gemm.cuh).
@@ -29,10 +30,10 @@ constexpr auto N = {N}, K = {K};
 constexpr auto BLOCK_M = {BLOCK_M};
 constexpr auto BLOCK_N = {BLOCK_N};
 constexpr auto kNumStages = {NUM_STAGES};
-constexpr auto kNumTMAMulticast = {NUM_TMA_MULTICAST};
+constexpr auto kNumCtasPerLoad = 1;
 
 // Make a templated GEMM
-using GemmType = Gemm<N, K, BLOCK_M, BLOCK_N, 128, 1, kNumStages, kNumTMAMulticast, GemmType::Normal>;
+using GemmType = Gemm<N, K, BLOCK_M, BLOCK_N, 128, 1, kNumStages, kNumCtasPerLoad, GemmType::Normal>;
 
 // Launch kernel
 auto tma_a_desc = GemmType::make_2d_tma_a_desc(lhs, m);
@@ -121,7 +122,7 @@ def gemm_fp8_fp8_bf16_nt(lhs: Tuple[torch.Tensor, torch.Tensor], rhs: Tuple[torc
         args = (lhs_q, lhs_scales, rhs_q, rhs_scales, out, m, torch.cuda.current_stream(), num_sms, smem_size)
         runtime = jit_tuner.compile_and_tune(
             name='gemm_fp8_fp8_bf16_nt',
-            keys={'N': n, 'K': k, 'BLOCK_M': 128, 'BLOCK_N': bn, 'NUM_STAGES': stages, 'NUM_TMA_MULTICAST': 1},
+            keys={'N': n, 'K': k, 'BLOCK_M': 128, 'BLOCK_N': bn, 'NUM_STAGES': stages},
             space=(), includes=includes, arg_defs=arg_defs, template=template, args=args)
         rc = runtime(*args)
         if rc != 0:
