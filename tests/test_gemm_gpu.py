@@ -67,6 +67,31 @@ def test_decode_shape(cuda_lib, m):
     _check(d.cpu(), ref.ref_gemm(lhs, rhs), f"decode m={m}")
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 128, 256), (16, 256, 512), (17, 384, 1024), (33, 128, 2048), (64, 7168, 2048),
+                                   (16, 7168, 2048), (64, 256, 256)])
+def test_weight_streaming_kernel(cuda_lib, m, n, k):
+    """block_n=1 forces the small-M kernel (swap-AB, split-K over a CTA pair); compare with the oracle and with
+    the general kernel."""
+    lhs, rhs = _operands(m, n, k, seed=m * 7 + k, outliers=True)
+    d_ref = ref.ref_gemm(lhs, rhs)
+    d_small = _run(lhs, rhs, block_n=1)
+    _check(d_small.cpu(), d_ref, f"small-M m={m} n={n} k={k}")
+    d_general = _run(lhs, rhs, block_n=64)
+    assert ref.rel_frobenius(d_small.cpu(), d_general.cpu()) <= 1e-3
+
+
+def test_weight_streaming_kernel_limits(cuda_lib):
+    import ctypes
+    from yan_b200 import _lib
+    p = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda").data_ptr()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    f = "yan_b200_gemm_fp8_fp8_bf16_nt"
+    assert _lib.call_rc(f, p, p, p, p, p, 128, 128, 256, 128, stream, sms, 1) == 1   # M > 64
+    assert _lib.call_rc(f, p, p, p, p, p, 16, 128, 128, 128, stream, sms, 1) == 1    # K not a multiple of 256
+    assert _lib.call_rc(f, p, p, p, p, p, 64, 128, 8192, 128, stream, sms, 1) == 1   # too many k-blocks for TMEM
+
+
 def test_long_k_many_tiles(cuda_lib):
     """More tiles than SMs and a long K loop: exercises ring wrap-around and persistent scheduling."""
     lhs, rhs = _operands(1024, 2560, 4096, seed=3)

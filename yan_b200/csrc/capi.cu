@@ -7,6 +7,7 @@
 
 #include "../../include/yan_b200.h"
 #include "gemm_dispatch.h"
+#include "gemm/fp8_gemm_small_m.cuh"
 #include "quant/fp8_cast.cuh"
 
 namespace {
@@ -84,6 +85,7 @@ int choose_block_n(int m, int n, int num_sms) {
 int dispatch_gemm(yan::GemmType type, yan::OutKind out_kind, yan::GemmArgs& a, int block_n, void* stream) {
     if (a.m == 0 || a.n == 0 || a.k == 0) return yan::kBadArgument;
     if (a.num_sms <= 0) return yan::kBadArgument;
+    const bool want_auto = (block_n == 0);
     if (block_n == 0) {
         const int rows = (type == yan::GemmType::GroupedMasked) ? static_cast<int>(a.m * a.num_groups) : static_cast<int>(a.m);
         block_n = choose_block_n(rows, static_cast<int>(a.n), a.num_sms);
@@ -91,6 +93,14 @@ int dispatch_gemm(yan::GemmType type, yan::OutKind out_kind, yan::GemmArgs& a, i
     a.status = status_word_of_current_device();
     a.timeout_ns = g_timeout_ns;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // M <= 64: the weight-streaming kernel (block_n 1 asks for it explicitly, 0 lets it win when it fits).
+    if (type == yan::GemmType::Normal && out_kind == yan::OutKind::BF16 && (want_auto || block_n == 1)) {
+        int dev = 0, max_smem = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        if (yan::small_m_supported(a.m, a.n, a.k, max_smem)) return yan::launch_fp8_gemm_small_m(a, s);
+        if (block_n == 1) return yan::kBadArgument;
+    }
     switch (block_n) {
         case 32: return yan::launch_gemm_bn32(type, out_kind, a, s);
         case 64: return yan::launch_gemm_bn64(type, out_kind, a, s);
