@@ -140,6 +140,17 @@ void yan_b200_fp8_linear_bf16_static(const void* a, const void* rhs, const void*
  */
 void yan_b200_read_device_status(int* status, int reset, int* return_code);
 
+/*
+ * Programmatic dependent launch for the weight-streaming (M <= 64) kernel.  When enabled, that kernel is
+ * launched with cudaLaunchAttributeProgrammaticStreamSerialization: its weight loads (rhs) may start while the
+ * previous kernel of the stream is still running; activations, scales of the activations and the output are
+ * only touched after the previous kernel has completed.  Enable it only when `rhs` / `rhs_scales` are not
+ * written by the kernel that precedes the GEMM in its stream (true for inference weights).  Default: off.
+ * No reference counterpart (the reference launches every kernel with plain <<<>>>, e.g.
+ * yan/include/gemm/cute_gemm.cuh:373).
+ */
+void yan_b200_set_programmatic_dependent_launch(int enabled);
+
 /* Sets the bound (nanoseconds, default 2e9) of every device-side wait of later GEMM launches. */
 void yan_b200_set_wait_timeout_ns(unsigned long long timeout_ns);
 

@@ -68,7 +68,7 @@ def test_decode_shape(cuda_lib, m):
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 128, 256), (16, 256, 512), (17, 384, 1024), (33, 128, 2048), (64, 7168, 2048),
-                                   (16, 7168, 2048), (64, 256, 256)])
+                                   (16, 7168, 2048), (64, 256, 256), (32, 512, 2560), (48, 256, 1536)])
 def test_weight_streaming_kernel(cuda_lib, m, n, k):
     """block_n=1 forces the small-M kernel (swap-AB, split-K over a CTA pair); compare with the oracle and with
     the general kernel."""
@@ -88,6 +88,7 @@ def test_weight_streaming_kernel_limits(cuda_lib):
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     f = "yan_b200_gemm_fp8_fp8_bf16_nt"
     assert _lib.call_rc(f, p, p, p, p, p, 128, 128, 256, 128, stream, sms, 1) == 1   # M > 64
+    assert _lib.call_rc(f, p, p, p, p, p, 16, 192, 256, 192, stream, sms, 1) == 1    # N not a multiple of 128
     assert _lib.call_rc(f, p, p, p, p, p, 16, 128, 128, 128, stream, sms, 1) == 1    # K not a multiple of 256
     assert _lib.call_rc(f, p, p, p, p, p, 64, 128, 8192, 128, stream, sms, 1) == 1   # too many k-blocks for TMEM
 

@@ -16,6 +16,7 @@ namespace {
 __device__ int g_status_word = 0;
 
 unsigned long long g_timeout_ns = 2000000000ull;
+int g_programmatic_launch = 0;
 
 constexpr int kMaxDevices = 64;
 int* g_status_ptr[kMaxDevices] = {};
@@ -98,7 +99,7 @@ int dispatch_gemm(yan::GemmType type, yan::OutKind out_kind, yan::GemmArgs& a, i
         int dev = 0, max_smem = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
-        if (yan::small_m_supported(a.m, a.n, a.k, max_smem)) return yan::launch_fp8_gemm_small_m(a, s);
+        if (yan::small_m_supported(a.m, a.n, a.k, max_smem)) return yan::launch_fp8_gemm_small_m(a, s, g_programmatic_launch != 0);
         if (block_n == 1) return yan::kBadArgument;
     }
     switch (block_n) {
@@ -279,6 +280,8 @@ YAN_EXPORT void yan_b200_read_device_status(int* status, int reset, int* return_
     }
     set_rc(return_code, yan::kOk);
 }
+
+YAN_EXPORT void yan_b200_set_programmatic_dependent_launch(int enabled) { g_programmatic_launch = enabled; }
 
 YAN_EXPORT void yan_b200_set_wait_timeout_ns(unsigned long long timeout_ns) {
     g_timeout_ns = timeout_ns == 0 ? 1 : timeout_ns;

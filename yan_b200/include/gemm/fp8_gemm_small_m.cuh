@@ -10,9 +10,18 @@
 //   * nothing is recycled: every k-block of a CTA has its own shared-memory tile, its own mbarrier and its
 //     own TMEM columns, so all TMA loads are issued at kernel start (the whole of B is in flight at once),
 //     the MMA thread never waits for the promotion warps and there is one commit at the end;
-//   * promotion happens once, after the last MMA: thread = weight row, acc[m] += sA[m,kb]*sB[kb]*P_kb[n,m];
+//   * each k-block is promoted as soon as its four MMAs are done (one commit and one mbarrier per k-block), so
+//     only the last k-block's promotion trails the weight stream: thread = weight row,
+//     acc[m] += sA[m,kb]*sB[kb]*P_kb[n,m];
+//   * programmatic dependent launch: the weight loads are issued before griddepcontrol.wait, everything that
+//     touches activations or the output after it; with the launch attribute set (see the host launcher) the
+//     weight loads of GEMM i+1 may start while GEMM i finishes.  Weights must therefore not be produced by the
+//     kernel that precedes the GEMM in the stream when that attribute is used;
 //   * the second CTA of a pair sends its fp32 partial through distributed shared memory (st.shared::cluster),
-//     the first adds its own and writes bf16.  No multicast, no remote global memory.
+//     the first adds its own and writes bf16.  No multicast, no remote global memory.  (Measured alternatives,
+//     all slower end to end: a 4-CTA cluster with bulk-copy exchange -- the partial sums then cross the
+//     SM-to-SM network at about 2 TB/s for the whole chip, a third of the weight bytes again at M = 64 -- and
+//     one-way mbarrier hand-shakes instead of the two cluster barriers: a remote arrive costs ~300 ns.)
 // Limits (checked on the host; otherwise the general kernel is used): N % 128 == 0, K % 256 == 0,
 // (K/256) * M_PAD <= 512 TMEM columns, (K/256) * (16384 + 128*M_PAD) bytes of shared memory.
 
@@ -39,7 +48,7 @@ __host__ __device__ inline SmallMSmem small_m_smem_layout(uint32_t m_pad, uint32
     s.off_x = s.off_w + (w_bytes > exchange_bytes ? w_bytes : exchange_bytes);  // kbh x [m_pad x 128 B] activation tiles
     s.off_scales = s.off_x + kbh * m_pad * 128u;  // kbh x m_pad floats: sA[m,kb] * sB[kb]
     s.off_barriers = align_up(s.off_scales + kbh * m_pad * 4u, 8u);
-    s.off_tmem_slot = s.off_barriers + (kSmallMMaxKBlocks + 1) * 8u;
+    s.off_tmem_slot = s.off_barriers + 2 * kSmallMMaxKBlocks * 8u;  // full[kb] and done[kb]
     s.off_abort = s.off_tmem_slot + 4;
     s.total = s.off_abort + 4 + 1024;
     return s;
@@ -64,6 +73,11 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta_
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank));
     return r;
 }
+__device__ __forceinline__ float ld_shared_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
@@ -82,7 +96,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kSmallMThreads, 1)
     const uint32_t kbh = num_k_blocks / 2;  // k-blocks of this CTA
     const SmallMSmem L = small_m_smem_layout(M_PAD, kbh);
     uint64_t* full_barriers = reinterpret_cast<uint64_t*>(smem + L.off_barriers);
-    uint64_t* done_barrier = full_barriers + kSmallMMaxKBlocks;
+    uint64_t* done_barriers = full_barriers + kSmallMMaxKBlocks;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L.off_tmem_slot);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L.off_abort);
     float* s_scales = reinterpret_cast<float*>(smem + L.off_scales);
@@ -94,23 +108,32 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kSmallMThreads, 1)
     const uint32_t kb_first = cta_rank * kbh;
     const uint32_t tmem_cols = small_m_tmem_cols(M_PAD, kbh);
 
+    // Let the next kernel of the stream begin its own weight loads right away.
+    ptx::grid_dependency_launch_dependents();
+
     if (warp_idx == 4) {
         if (lane_idx == 0) {
             ptx::tma_prefetch_desc(&tensor_map_w);
             ptx::tma_prefetch_desc(&tensor_map_x);
-            for (uint32_t i = 0; i < kbh; ++i) ptx::mbar_init(full_barriers + i, 1);
-            ptx::mbar_init(done_barrier, 1);
+            for (uint32_t i = 0; i < kbh; ++i) {
+                ptx::mbar_init(full_barriers + i, 1);
+                ptx::mbar_init(done_barriers + i, 1);
+            }
             *abort_flag = 0;
             ptx::fence_barrier_init();
             ptx::fence_proxy_async_smem();
             // Every load of this CTA goes out now: nothing below ever waits for a buffer to be recycled.
+            // Weights first: they are parameters, not products of the kernel before this one, so under
+            // programmatic dependent launch they may be fetched while that kernel is still running.
             for (uint32_t i = 0; i < kbh; ++i) {
                 ptx::mbar_arrive_expect_tx(full_barriers + i, 16384u + M_PAD * 128u);
                 ptx::tma_load_2d(smem + L.off_w + i * 16384u, &tensor_map_w, full_barriers + i,
                                  static_cast<int32_t>((kb_first + i) * kBlockK), static_cast<int32_t>(n_block * 128u));
+            }
+            ptx::grid_dependency_wait();  // activations and the output buffer belong to the stream order
+            for (uint32_t i = 0; i < kbh; ++i)
                 ptx::tma_load_2d(smem + L.off_x + i * M_PAD * 128u, &tensor_map_x, full_barriers + i,
                                  static_cast<int32_t>((kb_first + i) * kBlockK), 0);
-            }
         }
         __syncwarp();
         ptx::tmem_alloc(tmem_slot, tmem_cols);
@@ -118,6 +141,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kSmallMThreads, 1)
     } else {
         // Promotion warps: while the weights stream in, fold both scale factors of every (k-block, row) pair.
         const float* sb_ptr = p.scales_b + static_cast<size_t>(n_block) * num_k_blocks + kb_first;
+        ptx::grid_dependency_wait();
         for (uint32_t i = threadIdx.x; i < kbh * M_PAD; i += 128) {
             const uint32_t kb = i / M_PAD, m = i % M_PAD;
             const float sa = (m < p.shape_m) ? __ldg(p.scales_a + static_cast<size_t>(kb_first + kb) * p.sa_ld + m) : 0.0f;
@@ -146,18 +170,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kSmallMThreads, 1)
                 for (uint32_t k = 0; k < kBlockK / kUmmaK; ++k)
                     ptx::umma_f8f6f4_ss(tmem_base + i * M_PAD, w_desc + k * kDescKStep, x_desc + k * kDescKStep, idesc,
                                         k > 0);
+                ptx::umma_commit(done_barriers + i);  // this k-block's partial product can be promoted
             }
-            ptx::umma_commit(done_barrier);
         }
         __syncwarp();
     } else {
-        const bool ok = detail::bounded_wait(done_barrier, 0, abort_flag, p, 6);
-        alive = __all_sync(0xffffffffu, ok);
-        if (alive) {
-            ptx::tcgen05_fence_after_thread_sync();
-            const uint32_t taddr = tmem_base + ((warp_idx * 32u) << 16);
-            constexpr uint32_t kChunk = M_PAD < 32 ? M_PAD : 32;
-            for (uint32_t i = 0; i < kbh; ++i) {
+        const uint32_t taddr = tmem_base + ((warp_idx * 32u) << 16);
+        constexpr uint32_t kChunk = M_PAD < 32 ? M_PAD : 32;
+        for (uint32_t i = 0; i < kbh && alive; ++i) {
+            const bool ok = detail::bounded_wait(done_barriers + i, 0, abort_flag, p, 6);
+            alive = __all_sync(0xffffffffu, ok);
+            if (alive) {
+                ptx::tcgen05_fence_after_thread_sync();
 #pragma unroll
                 for (uint32_t c = 0; c < M_PAD / kChunk; ++c) {
                     uint32_t t[kChunk];
@@ -169,8 +193,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kSmallMThreads, 1)
                                                    acc[c * kChunk + j]);
                 }
             }
-            ptx::tcgen05_fence_before_thread_sync();
         }
+        ptx::tcgen05_fence_before_thread_sync();
     }
 
     // Both CTAs of the pair are past their MMAs and TMEM reads: the weight tiles of CTA 0 are dead and become
@@ -187,12 +211,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kSmallMThreads, 1)
     ptx::cluster_arrive();
     ptx::cluster_wait();
     if (warp_idx < 4 && cta_rank == 0 && alive && *abort_flag == 0) {
+        // Two phases, so that no global store sits between the shared-memory loads (with stores in the loop the
+        // compiler keeps load(m+1) behind store(m) and every row pays a full shared-memory latency).
+        const uint32_t ex = ptx::smem_u32(exchange) + n_in_tile * 4u;
+#pragma unroll
+        for (uint32_t m = 0; m < M_PAD; ++m) acc[m] += ptx::ld_shared_f32(ex + m * 512u);
         __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + n_block * 128u + n_in_tile;
 #pragma unroll
-        for (uint32_t m = 0; m < M_PAD; ++m) {
-            if (m < p.shape_m)
-                out[static_cast<size_t>(m) * p.ldd] = __float2bfloat16_rn(acc[m] + exchange[m * 128u + n_in_tile]);
-        }
+        for (uint32_t m = 0; m < M_PAD; ++m)
+            if (m < p.shape_m) out[static_cast<size_t>(m) * p.ldd] = __float2bfloat16_rn(acc[m]);
     }
 
     ptx::tcgen05_fence_before_thread_sync();
@@ -215,7 +242,7 @@ inline bool small_m_supported(uint32_t m, uint32_t n, uint32_t k, int max_smem) 
 
 template <uint32_t M_PAD>
 inline int launch_small_m_instance(const GemmParams& p, const CUtensorMap& map_w, const CUtensorMap& map_x,
-                                   uint32_t smem_bytes, uint32_t grid, cudaStream_t stream) {
+                                   uint32_t smem_bytes, uint32_t grid, cudaStream_t stream, bool programmatic) {
     auto kernel = fp8_gemm_small_m_kernel<M_PAD>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) {
         cudaGetLastError();
@@ -226,8 +253,11 @@ inline int launch_small_m_instance(const GemmParams& p, const CUtensorMap& map_w
     cfg.blockDim = dim3(kSmallMThreads);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
-    cfg.attrs = nullptr;  // the cluster shape is compiled into the kernel (__cluster_dims__)
-    cfg.numAttrs = 0;
+    cudaLaunchAttribute attr[1];  // the cluster shape is compiled into the kernel (__cluster_dims__)
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, p, map_w, map_x);
     if (e != cudaSuccess) {
         cudaGetLastError();
@@ -237,7 +267,7 @@ inline int launch_small_m_instance(const GemmParams& p, const CUtensorMap& map_w
 }
 
 // Host launcher.  Arguments as GemmLauncher::launch (Normal GEMM, bf16 output).
-inline int launch_fp8_gemm_small_m(const GemmArgs& a, cudaStream_t stream) {
+inline int launch_fp8_gemm_small_m(const GemmArgs& a, cudaStream_t stream, bool programmatic = false) {
     if (a.lhs == nullptr || a.lhs_scales == nullptr || a.rhs == nullptr || a.rhs_scales == nullptr || a.out == nullptr)
         return kBadArgument;
     if (a.ldd < a.n || a.lhs_scales_ld < a.m) return kBadArgument;
@@ -270,9 +300,9 @@ inline int launch_fp8_gemm_small_m(const GemmArgs& a, cudaStream_t stream) {
     const uint32_t smem_bytes = small_m_smem_layout(m_pad, kbh).total;
     const uint32_t grid = 2 * (a.n / 128);
     switch (m_pad) {
-        case 16: return launch_small_m_instance<16>(p, map_w, map_x, smem_bytes, grid, stream);
-        case 32: return launch_small_m_instance<32>(p, map_w, map_x, smem_bytes, grid, stream);
-        default: return launch_small_m_instance<64>(p, map_w, map_x, smem_bytes, grid, stream);
+        case 16: return launch_small_m_instance<16>(p, map_w, map_x, smem_bytes, grid, stream, programmatic);
+        case 32: return launch_small_m_instance<32>(p, map_w, map_x, smem_bytes, grid, stream, programmatic);
+        default: return launch_small_m_instance<64>(p, map_w, map_x, smem_bytes, grid, stream, programmatic);
     }
 }
 

@@ -27,6 +27,14 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
     return t;
 }
 
+// Programmatic dependent launch: `wait` blocks until the grids this one depends on have completed and
+// their memory is visible (no-op for an ordinary launch); `launch_dependents` lets the next grid of
+// the stream start its own pre-`wait` part early.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------------------------

@@ -225,6 +225,12 @@ def fp8_linear_workspace_bytes(m: int, k: int) -> int:
     return int(_lib.lib().yan_b200_fp8_linear_workspace_bytes(m, k))
 
 
+def set_programmatic_dependent_launch(enabled: bool) -> None:
+    """Lets the M <= 64 weight-streaming kernel start fetching weights while the previous kernel of the stream is
+    still running (programmatic dependent launch).  Only valid when the weights are not produced by that kernel."""
+    _lib.lib().yan_b200_set_programmatic_dependent_launch(int(bool(enabled)))
+
+
 def read_device_status(reset: bool = True) -> int:
     """Synchronises and returns the device status word (0 = no bounded wait ever ran out)."""
     status = ctypes.c_int(0)
