@@ -134,7 +134,7 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     static_assert(RegisterBudgetCheck<BLOCK_N>::ok);
     constexpr uint32_t kColsPerWG = BLOCK_N / kNumMathWGs;
     constexpr uint32_t kNumMathWarps = 4 * kNumMathWGs;
-    constexpr uint32_t kMaxChunk = (kNumMathWGs == 4) ? 16 : 32;             // 112 registers leave room for 16
+    constexpr uint32_t kMaxChunk = (kNumMathWGs == 4) ? 16 : 32;  // 112 registers leave little room
     constexpr uint32_t kChunk = kColsPerWG < kMaxChunk ? kColsPerWG : kMaxChunk;  // columns per tcgen05.ld
     constexpr uint32_t kNumChunks = kColsPerWG / kChunk;
     // With 4 warpgroups the other warps of the sub-partition hide a warp's TMEM-load latency and the
@@ -329,7 +329,8 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
                             }
 #pragma unroll
                             for (uint32_t j = 0; j < kChunk; ++j)
-                                acc[c * kChunk + j] = fmaf(scale, __uint_as_float(cur[j]), acc[c * kChunk + j]);
+                                acc[c * kChunk + j] =
+                                    fmaf(scale, __uint_as_float(cur[j]), acc[c * kChunk + j]);
                             if (c + 1 < kNumChunks) ptx::tmem_ld_wait<kChunk>(nxt);
                         }
                     } else {
@@ -345,7 +346,8 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
                             }
 #pragma unroll
                             for (uint32_t j = 0; j < kChunk; ++j)
-                                acc[c * kChunk + j] = fmaf(scale, __uint_as_float(t[j]), acc[c * kChunk + j]);
+                                acc[c * kChunk + j] =
+                                    fmaf(scale, __uint_as_float(t[j]), acc[c * kChunk + j]);
                         }
                     }
                     if (++buf == kNumTmemBufs) {

@@ -19,8 +19,8 @@ namespace yan {
 // warps 4..   : promotion/epilogue warpgroups; warpgroup h owns output columns
 //               [h*BLOCK_N/G, (h+1)*BLOCK_N/G) of the tile, warp (w%4) owns TMEM lanes 32*(w%4)..+31.
 // G = 2 everywhere.  G = 4 (sixteen promotion warps, 64 columns each, 112 registers) was measured slower
-// for BLOCK_N = 256: all promotion warps are released by the same barrier, so they load in lockstep and
-// then issue FMAs in lockstep, and extra warps add contention instead of overlap.
+// for BLOCK_N = 256 (851 vs 805 cycles per k-block): all promotion warps are released by the same barrier, so
+// they load TMEM in lockstep and then issue FMAs in lockstep, and extra warps add contention, not overlap.
 constexpr uint32_t kNumControlThreads = 128;
 constexpr uint32_t kNumMathThreadsPerGroup = 128;
 
