@@ -51,44 +51,88 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples the SM clock and the throttle reasons of one GPU while the timed region runs.  Reads only
+    (NVML queries every few milliseconds from a thread); falls back to nvidia-smi when NVML is not importable."""
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
-    def __init__(self, device_index: int) -> None:
-        self.rows = []
-        self.proc = None
-        self.thread = None
+    def __init__(self, device_index: int, period_s: float = 0.003) -> None:
         self.device_index = device_index
+        self.period_s = period_s
+        self.samples = []
+        self.reason_bits = 0
+        self.max_mhz = None
+        self.thread = None
+        self.stop_flag = threading.Event()
+        self.smi = None
+
+    def _physical_index(self) -> int:
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if self.device_index < len(ids) and ids[self.device_index].isdigit():
+                return int(ids[self.device_index])
+        return self.device_index
 
     def start(self) -> None:
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.device_index), "-lms", "100"],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
-            return
-        self.thread = threading.Thread(target=self._pump, daemon=True)
-        self.thread.start()
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.nvml = None
+            self._start_smi()
 
-    def _pump(self) -> None:
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.strip().split(",")])
+    def _poll(self) -> None:
+        nv = self.nvml
+        while not self.stop_flag.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)
+                bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                self.samples.append((time.perf_counter(), float(mhz)))
+                self.reason_bits |= int(bits)
+            except Exception:
+                pass
+            time.sleep(self.period_s)
 
-    def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.25)
-        self.proc.terminate()
+    def _start_smi(self) -> None:
+        query = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+                 "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+                 "clocks_event_reasons.sw_power_cap")
         try:
-            self.proc.wait(timeout=5)
+            self.smi = subprocess.Popen(["nvidia-smi", f"--query-gpu={query}", "--format=csv,noheader,nounits", "-i",
+                                         str(self._physical_index()), "-lms", "50"], stdout=subprocess.PIPE,
+                                        stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.smi = None
+
+    def stop(self, t_begin: float = None, t_end: float = None) -> dict:
+        """Median SM clock of the samples taken between t_begin and t_end (perf_counter stamps of the timed region)."""
+        if self.thread is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            inside = [m for (t, m) in self.samples if (t_begin is None or t >= t_begin) and (t_end is None or t <= t_end)]
+            use = inside if inside else [m for (_, m) in self.samples]
+            reasons = sorted(k for k, bit in self.REASONS.items() if self.reason_bits & bit)
+            return {"sm_mhz": statistics.median(use) if use else None, "sm_max_mhz": self.max_mhz,
+                    "samples_in_timed_region": len(inside), "samples": len(self.samples), "reasons": reasons,
+                    "source": "nvml"}
+        if self.smi is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock source available"]}
+        time.sleep(0.2)
+        self.smi.terminate()
+        try:
+            out, _ = self.smi.communicate(timeout=5)
         except subprocess.TimeoutExpired:
-            self.proc.kill()
+            self.smi.kill()
+            out = ""
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for line in out.splitlines():
+            r = [c.strip() for c in line.split(",")]
             if len(r) < 9:
                 continue
             try:
@@ -100,7 +144,7 @@ class ClockSampler:
                 if flag.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi"}
 
 
 def dist_setup(n_gpus: int):
@@ -209,6 +253,46 @@ def bench_dense(name: str, m: int, n: int, k: int, peaks, iters: int = 10) -> di
             "quant_frac_of_measured_hbm": qbytes / tq / 1e9 / peaks["hbm_gbs"]}
 
 
+def bench_k_split(rank: int, world: int, dist, steps: int = 10) -> dict:
+    """Row-parallel GEMM + allreduce (M=4096, N=8192, K=28672 split along K over the ranks): per step each rank
+    quantizes its K shard of A, computes a full-size bf16 partial D in row chunks and sums the partials with an NCCL
+    allreduce that overlaps the next chunk's GEMM.  Time = max over ranks, device events."""
+    import yan_b200
+    from yan_b200.comm import gemm_allreduce as ga
+    m, n, k = 4096, 8192, 28672
+    ks = k // world
+    g = torch.Generator(device="cuda").manual_seed(7)
+    a = torch.randn(m, k, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)[:, rank * ks:(rank + 1) * ks].contiguous()
+    gb = torch.Generator(device="cuda").manual_seed(70 + rank)
+    b = (torch.randn(n, ks, generator=gb, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    rhs = yan_b200.per_block_cast_to_fp8(b)
+    del b
+    lhs = yan_b200.per_token_cast_to_fp8(a)
+    out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    comm_stream = torch.cuda.Stream()
+    results = {}
+    for label, chunks in (("single allreduce", 1), ("4 row chunks overlapped", 4)):
+        def step():
+            yan_b200.per_token_cast_to_fp8(a, out=lhs)
+            ga.gemm_k_split_allreduce(lhs, rhs, out, partial_dtype=torch.bfloat16, num_chunks=chunks, comm_stream=comm_stream)
+        for _ in range(3):
+            step()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        results[label] = {"ms_per_step": t.item(), "TFLOP/s": 2.0 * m * n * k / (t.item() / 1e3) / 1e12}
+    return {"workload": f"C5 row-parallel GEMM + allreduce M={m} N={n} K={k} (K/{world} per GPU, bf16 partials, NCCL)",
+            "allreduce_bytes": 2 * m * n, **results}
+
+
 def cpu_reference_step(a_slab, rhs_cpu):
     """The CPU dequantize-and-matmul path on one slab: quantize A, dequantize both, fp32 matmul, bf16."""
     from oracle import ref
@@ -280,11 +364,12 @@ def run_ours(args) -> None:
     # ---- timed region: exactly K steps; per-kernel events on the launching (current) stream ----
     sampler = ClockSampler(local)
     sampler.start()
-    time.sleep(0.3)
+    time.sleep(0.05)
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     barrier()
     t_start = torch.cuda.Event(enable_timing=True)
     t_end = torch.cuda.Event(enable_timing=True)
+    wall_begin = time.perf_counter()
     t_start.record()
     for i in range(args.steps):
         ev[i][0].record()
@@ -294,7 +379,7 @@ def run_ours(args) -> None:
         ev[i][2].record()
     t_end.record()
     barrier()
-    clocks = sampler.stop()
+    clocks = sampler.stop(wall_begin, time.perf_counter())
     elapsed_ms = t_start.elapsed_time(t_end)
     quant_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
     gemm_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
@@ -372,6 +457,10 @@ def run_ours(args) -> None:
     del a_host, out_host, a_dev, out, lhs, rhs, a
     torch.cuda.empty_cache()
 
+    if world > 1 and not args.no_extras:
+        k_split = bench_k_split(rank, world, dist)
+        if rank == 0:
+            line["other_workloads"] = [k_split]
     if rank == 0 and world == 1 and not args.no_extras:
         extras = []
         for m_small in (16, 64):
