@@ -160,3 +160,21 @@ def test_gemm_rejects_bad_arguments(cuda_lib):
     assert _lib.call_rc(f, p + 8, p, p, p, p, 128, 128, 128, 128, stream, sms, 0) == 1  # misaligned lhs
     assert _lib.call_rc(f, None, p, p, p, p, 128, 128, 128, 128, stream, sms, 0) == 1   # null
     assert _lib.call_rc(f, p, p, p, p, p, 0, 128, 128, 128, stream, sms, 0) == 1        # empty M
+
+
+def test_host_front_end_pipelines_three_calls(cuda_lib):
+    """HostFp8Linear: pinned host in, pinned host out, rotating device slots; each call checked against the oracle."""
+    import yan_b200
+    m, n, k = 192, 512, 1024
+    _, b = ref.make_inputs(m, n, k, seed=40)
+    rhs = ref.per_block_cast_to_fp8(b)
+    pipe = yan_b200.HostFp8Linear((rhs[0].cuda(), rhs[1].cuda()), m, depth=2)
+    ins, outs = [], []
+    for i in range(3):
+        a, _ = ref.make_inputs(m, 128, k, seed=41 + i)
+        ins.append(a.pin_memory())
+        outs.append(torch.empty(m, n, dtype=torch.bfloat16).pin_memory())
+        pipe.submit(ins[-1], outs[-1])
+    pipe.wait()
+    for a, o in zip(ins, outs):
+        _check(o, ref.ref_gemm(ref.per_token_cast_to_fp8(a), rhs), "host front end")

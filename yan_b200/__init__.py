@@ -12,6 +12,7 @@ from .jit_kernels import (ceil_div, fp8_linear, fp8_linear_workspace_bytes, gemm
                           m_grouped_gemm_fp8_fp8_bf16_nt_contiguous, m_grouped_gemm_fp8_fp8_bf16_nt_masked,
                           per_block_cast_to_fp8, per_token_cast_to_fp8, read_device_status, set_num_sms,
                           set_programmatic_dependent_launch)
+from .jit_kernels import HostFp8Linear
 from .utils import bench_events, bench_kineto, calc_diff, count_bytes
 
 __version__ = "0.1.0"

@@ -329,8 +329,7 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
                             }
 #pragma unroll
                             for (uint32_t j = 0; j < kChunk; ++j)
-                                acc[c * kChunk + j] =
-                                    fmaf(scale, __uint_as_float(cur[j]), acc[c * kChunk + j]);
+                                acc[c * kChunk + j] = fmaf(scale, __uint_as_float(cur[j]), acc[c * kChunk + j]);
                             if (c + 1 < kNumChunks) ptx::tmem_ld_wait<kChunk>(nxt);
                         }
                     } else {
@@ -346,8 +345,7 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
                             }
 #pragma unroll
                             for (uint32_t j = 0; j < kChunk; ++j)
-                                acc[c * kChunk + j] =
-                                    fmaf(scale, __uint_as_float(t[j]), acc[c * kChunk + j]);
+                                acc[c * kChunk + j] = fmaf(scale, __uint_as_float(t[j]), acc[c * kChunk + j]);
                         }
                     }
                     if (++buf == kNumTmemBufs) {
