@@ -137,9 +137,6 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     constexpr uint32_t kMaxChunk = (kNumMathWGs == 4) ? 16 : 32;  // 112 registers leave little room
     constexpr uint32_t kChunk = kColsPerWG < kMaxChunk ? kColsPerWG : kMaxChunk;  // columns per tcgen05.ld
     constexpr uint32_t kNumChunks = kColsPerWG / kChunk;
-    // With 4 warpgroups the other warps of the sub-partition hide a warp's TMEM-load latency and the
-    // register budget (120) has no room for a second landing buffer; with 2 the loads are double-buffered.
-    constexpr bool kDoubleBuffer = (kNumMathWGs == 2) && (kNumChunks > 1);
     constexpr uint32_t kScaleDepth = (kNumMathWGs == 4) ? 2 : 4;
 
     extern __shared__ uint8_t smem_raw[];
@@ -312,41 +309,22 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
 
                     // Chunks of kChunk columns move TMEM -> registers.  The TMEM buffer is handed back as soon
                     // as the last chunk has landed, before its FMAs.
-                    if constexpr (kDoubleBuffer) {
-                        uint32_t t0[kChunk], t1[kChunk];
-                        ptx::tmem_ld_32x32b<kChunk>(taddr, t0);
-                        ptx::tmem_ld_wait<kChunk>(t0);
+                    // Nothing is scheduled between a tcgen05.ld and its wait: FMAs issued while a load is
+                    // outstanding were measured ~10x slower than after it (the load does not overlap with the
+                    // issuing warp's own arithmetic), so a second landing buffer buys nothing.
 #pragma unroll
-                        for (uint32_t c = 0; c < kNumChunks; ++c) {
-                            uint32_t(&cur)[kChunk] = (c & 1) ? t1 : t0;
-                            uint32_t(&nxt)[kChunk] = (c & 1) ? t0 : t1;
-                            if (c + 1 < kNumChunks) {
-                                ptx::tmem_ld_32x32b<kChunk>(taddr + (c + 1) * kChunk, nxt);
-                            } else {
-                                ptx::tcgen05_fence_before_thread_sync();
-                                __syncwarp();
-                                if (lane_idx == 0) ptx::mbar_arrive(tmem_empty_barriers + buf);
-                            }
-#pragma unroll
-                            for (uint32_t j = 0; j < kChunk; ++j)
-                                acc[c * kChunk + j] = fmaf(scale, __uint_as_float(cur[j]), acc[c * kChunk + j]);
-                            if (c + 1 < kNumChunks) ptx::tmem_ld_wait<kChunk>(nxt);
+                    for (uint32_t c = 0; c < kNumChunks; ++c) {
+                        uint32_t t[kChunk];
+                        ptx::tmem_ld_32x32b<kChunk>(taddr + c * kChunk, t);
+                        ptx::tmem_ld_wait<kChunk>(t);
+                        if (c + 1 == kNumChunks) {
+                            ptx::tcgen05_fence_before_thread_sync();
+                            __syncwarp();
+                            if (lane_idx == 0) ptx::mbar_arrive(tmem_empty_barriers + buf);
                         }
-                    } else {
 #pragma unroll
-                        for (uint32_t c = 0; c < kNumChunks; ++c) {
-                            uint32_t t[kChunk];
-                            ptx::tmem_ld_32x32b<kChunk>(taddr + c * kChunk, t);
-                            ptx::tmem_ld_wait<kChunk>(t);
-                            if (c + 1 == kNumChunks) {
-                                ptx::tcgen05_fence_before_thread_sync();
-                                __syncwarp();
-                                if (lane_idx == 0) ptx::mbar_arrive(tmem_empty_barriers + buf);
-                            }
-#pragma unroll
-                            for (uint32_t j = 0; j < kChunk; ++j)
-                                acc[c * kChunk + j] = fmaf(scale, __uint_as_float(t[j]), acc[c * kChunk + j]);
-                        }
+                        for (uint32_t j = 0; j < kChunk; ++j)
+                            acc[c * kChunk + j] = fmaf(scale, __uint_as_float(t[j]), acc[c * kChunk + j]);
                     }
                     if (++buf == kNumTmemBufs) {
                         buf = 0;
