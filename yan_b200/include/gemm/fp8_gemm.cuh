@@ -311,7 +311,9 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
                     // as the last chunk has landed, before its FMAs.
                     // Nothing is scheduled between a tcgen05.ld and its wait: FMAs issued while a load is
                     // outstanding were measured ~10x slower than after it (the load does not overlap with the
-                    // issuing warp's own arithmetic), so a second landing buffer buys nothing.
+                    // issuing warp's own arithmetic), so a second landing buffer buys nothing.  Also measured and
+                    // slower: postponing warpgroup 1's last chunk to its next k-block so that the two warps of
+                    // a sub-partition alternate between loading and multiplying (1.93 vs 2.17 PFLOP/s on C4).
 #pragma unroll
                     for (uint32_t c = 0; c < kNumChunks; ++c) {
                         uint32_t t[kChunk];
