@@ -141,6 +141,14 @@ void yan_b200_fp8_linear_bf16_static(const void* a, const void* rhs, const void*
 void yan_b200_read_device_status(int* status, int reset, int* return_code);
 
 /*
+ * Self-test of the bounded-wait machinery: launches one tiny kernel whose only thread waits (at most timeout_ns,
+ * <= 1 s) on an mbarrier nothing arrives on, so the wait runs out, the status word becomes
+ * (YAN_B200_DEVICE_TIMEOUT << 8) | 15 and the kernel returns normally.  No counterpart in the reference (it has no
+ * device-side waits outside CUTLASS).
+ */
+void yan_b200_wait_probe(unsigned long long timeout_ns, void* stream, int* return_code);
+
+/*
  * Programmatic dependent launch for the weight-streaming (M <= 64) kernel.  When enabled, that kernel is
  * launched with cudaLaunchAttributeProgrammaticStreamSerialization: its weight loads (rhs) may start while the
  * previous kernel of the stream is still running; activations, scales of the activations and the output are

@@ -34,6 +34,7 @@ SIGNATURES = {
     "yan_b200_fp8_linear_bf16": (None, [_P, _P, _P, _P, _P, ctypes.c_size_t, _I, _I, _I, _I, _P, _I, _I, _RC]),
     "yan_b200_fp8_linear_bf16_static": (None, [_P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _RC]),
     "yan_b200_read_device_status": (None, [_RC, _I, _RC]),
+    "yan_b200_wait_probe": (None, [ctypes.c_ulonglong, _P, _RC]),
     "yan_b200_set_programmatic_dependent_launch": (None, [_I]),
     "yan_b200_set_wait_timeout_ns": (None, [ctypes.c_ulonglong]),
 }

@@ -59,6 +59,21 @@ unsigned char* static_scratch_of_current_device() {
     return g_static_scratch_ptr[dev];
 }
 
+// Diagnostic kernel: one thread waits, with the same bounded wait the GEMMs use, on an mbarrier that nothing
+// ever arrives on.  The wait runs out, the status word is written, the kernel returns.
+__global__ void wait_probe_kernel(yan::GemmParams p) {
+    __shared__ uint64_t bar;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        yan::ptx::mbar_init(&bar, 1);
+        abort_flag = 0;
+        yan::ptx::fence_barrier_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) yan::detail::bounded_wait(&bar, 0, &abort_flag, p, 15);
+    __syncthreads();
+}
+
 inline void set_rc(int* rc, int v) {
     if (rc != nullptr) *rc = v;
 }
@@ -279,6 +294,16 @@ YAN_EXPORT void yan_b200_read_device_status(int* status, int reset, int* return_
         }
     }
     set_rc(return_code, yan::kOk);
+}
+
+YAN_EXPORT void yan_b200_wait_probe(unsigned long long timeout_ns, void* stream, int* return_code) {
+    yan::GemmParams p = {};
+    p.status = status_word_of_current_device();
+    p.timeout_ns = timeout_ns == 0 ? 1 : timeout_ns;
+    if (p.status == nullptr) return set_rc(return_code, yan::kLaunchFailed);
+    if (p.timeout_ns > 1000000000ull) return set_rc(return_code, yan::kBadArgument);  // a probe waits at most 1 s
+    wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    set_rc(return_code, cudaGetLastError() == cudaSuccess ? yan::kOk : yan::kLaunchFailed);
 }
 
 YAN_EXPORT void yan_b200_set_programmatic_dependent_launch(int enabled) { g_programmatic_launch = enabled; }
