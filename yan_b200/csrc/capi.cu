@@ -98,7 +98,8 @@ int choose_block_n(int m, int n, int num_sms) {
     return best;
 }
 
-int dispatch_gemm(yan::GemmType type, yan::OutKind out_kind, yan::GemmArgs& a, int block_n, void* stream) {
+int dispatch_gemm(yan::GemmType type, yan::OutKind out_kind, yan::GemmArgs& a, int block_n, void* stream,
+                  bool after_own_quantizer = false) {
     if (a.m == 0 || a.n == 0 || a.k == 0) return yan::kBadArgument;
     if (a.num_sms <= 0) return yan::kBadArgument;
     const bool want_auto = (block_n == 0);
@@ -114,7 +115,7 @@ int dispatch_gemm(yan::GemmType type, yan::OutKind out_kind, yan::GemmArgs& a, i
         int dev = 0, max_smem = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
-        if (yan::small_m_supported(a.m, a.n, a.k, max_smem)) return yan::launch_fp8_gemm_small_m(a, s, g_programmatic_launch != 0);
+        if (yan::small_m_supported(a.m, a.n, a.k, max_smem)) return yan::launch_fp8_gemm_small_m(a, s, g_programmatic_launch != 0 || after_own_quantizer);
         if (block_n == 1) return yan::kBadArgument;
     }
     switch (block_n) {
@@ -127,6 +128,25 @@ int dispatch_gemm(yan::GemmType type, yan::OutKind out_kind, yan::GemmArgs& a, i
 }
 
 bool positive(int a, int b, int c) { return a > 0 && b > 0 && c > 0; }
+
+// The GEMM of a quantize-then-GEMM call.  Its predecessor in the stream is this library's own quantizer, which never
+// writes weights, so the weight-streaming kernel (M <= 64) is always launched with programmatic stream serialization
+// here: its weight loads run while the quantizer does, and it waits for the quantizer before reading the activations.
+int gemm_after_quantizer(const void* q, const float* scales, const void* rhs, const void* rhs_scales, void* out, int m,
+                         int n, int k, int ldd, void* stream, int num_sms, int block_n) {
+    if (ldd <= 0) return yan::kBadArgument;
+    yan::GemmArgs a;
+    a.lhs = q;
+    a.lhs_scales = scales;
+    a.lhs_scales_ld = static_cast<uint32_t>(m);
+    a.rhs = rhs;
+    a.rhs_scales = static_cast<const float*>(rhs_scales);
+    a.out = out;
+    a.ldd = static_cast<uint32_t>(ldd);
+    a.m = m, a.n = n, a.k = k;
+    a.num_sms = num_sms;
+    return dispatch_gemm(yan::GemmType::Normal, yan::OutKind::BF16, a, block_n, stream, true);
+}
 
 }  // namespace
 
@@ -259,7 +279,7 @@ YAN_EXPORT void yan_b200_fp8_linear_bf16(const void* a, const void* rhs, const v
     float* scales = reinterpret_cast<float*>(q + yan::align_up(static_cast<size_t>(m) * k, static_cast<size_t>(256)));
     int rc = yan::launch_per_token_cast_to_fp8(a, q, scales, m, k, k, m, static_cast<cudaStream_t>(stream));
     if (rc != yan::kOk) return set_rc(return_code, rc);
-    yan_b200_gemm_fp8_fp8_bf16_nt(q, scales, rhs, rhs_scales, out, m, n, k, ldd, stream, num_sms, block_n, return_code);
+    set_rc(return_code, gemm_after_quantizer(q, scales, rhs, rhs_scales, out, m, n, k, ldd, stream, num_sms, block_n));
 }
 
 YAN_EXPORT void yan_b200_fp8_linear_bf16_static(const void* a, const void* rhs, const void* rhs_scales, void* out,
@@ -275,7 +295,7 @@ YAN_EXPORT void yan_b200_fp8_linear_bf16_static(const void* a, const void* rhs, 
     float* scales = reinterpret_cast<float*>(scratch + kStaticScratchQBytes);
     const int rc = yan::launch_per_token_cast_to_fp8(a, q, scales, m, k, k, m, static_cast<cudaStream_t>(stream));
     if (rc != yan::kOk) return set_rc(return_code, rc);
-    yan_b200_gemm_fp8_fp8_bf16_nt(q, scales, rhs, rhs_scales, out, m, n, k, ldd, stream, num_sms, block_n, return_code);
+    set_rc(return_code, gemm_after_quantizer(q, scales, rhs, rhs_scales, out, m, n, k, ldd, stream, num_sms, block_n));
 }
 
 YAN_EXPORT void yan_b200_read_device_status(int* status, int reset, int* return_code) {

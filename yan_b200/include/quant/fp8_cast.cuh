@@ -63,6 +63,9 @@ __global__ void __launch_bounds__(256) per_token_cast_to_fp8_kernel(const __nv_b
     constexpr uint32_t kGroups = 4;
     constexpr uint32_t kItems = kRows * kGroups / 16;  // per half-warp
     __shared__ float s_scales[kGroups][kRows];
+    // A GEMM launched behind this kernel with programmatic stream serialization may start its weight loads now;
+    // it waits for this grid to complete before it touches the quantized activations.  No effect otherwise.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     const uint32_t hw = threadIdx.x / 16, l = threadIdx.x % 16;
     const uint32_t row0 = blockIdx.y * kRows, kb0 = blockIdx.x * kGroups;
