@@ -81,3 +81,33 @@ def test_bench_kineto_finds_the_gemm_kernel(cuda_lib):
     t = yan_b200.bench_kineto(lambda: yan_b200.gemm_fp8_fp8_bf16_nt(lhs, rhs, out), "fp8_gemm_kernel", num_tests=5,
                               suppress_kineto_output=True)
     assert 0 < t < 1e-3
+
+
+def test_tuner_times_a_space_and_remembers_the_winner(cuda_lib, tmp_path, monkeypatch):
+    """compile_and_tune over several tile widths: every candidate is built, launched (non-zero return codes are
+    skipped), timed, and the winner is stored in tuned.json so that a new tuner does not time again."""
+    import json
+    import yan_b200
+    from yan_b200.jit import compiler
+    from yan_b200.jit_kernels.tuner import JITTuner
+    monkeypatch.setenv("YAN_CACHE_DIR", str(tmp_path))
+    monkeypatch.setenv("YAN_FP8_GEMM_JIT", "1")
+    monkeypatch.setenv("YAN_FP8_GEMM_TUNE", "1")
+    compiler.get_default_user_dir.cache_clear()
+    try:
+        a, b = ref.make_inputs(128, 128, 512, seed=2)      # N = 128: the space is BLOCK_N in {128, 64, 32}
+        lhs, rhs = ref.per_token_cast_to_fp8(a), ref.per_block_cast_to_fp8(b)
+        out = torch.empty(128, 128, dtype=torch.bfloat16, device="cuda")
+        yan_b200.gemm_fp8_fp8_bf16_nt((lhs[0].cuda(), lhs[1].t().contiguous().cuda().t()), (rhs[0].cuda(), rhs[1].cuda()), out)
+        torch.cuda.synchronize()
+        assert ref.rel_frobenius(out.cpu(), ref.ref_gemm(lhs, rhs)) <= 1e-3
+        built = [d for d in os.listdir(os.path.join(tmp_path, "cache")) if d.startswith("kernel.gemm_fp8_fp8_bf16_nt.")]
+        assert len(built) == 3
+        with open(os.path.join(tmp_path, "cache", "tuned.json")) as f:
+            stored = json.load(f)
+        assert len(stored) == 1 and list(stored.values())[0]["BLOCK_N"] in (128, 64, 32)
+        # a fresh tuner (new process in real life) goes straight to the remembered configuration
+        fresh = JITTuner()
+        assert fresh._load_choice(list(stored.keys())[0]) == list(stored.values())[0]
+    finally:
+        compiler.get_default_user_dir.cache_clear()

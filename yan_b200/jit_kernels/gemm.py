@@ -6,7 +6,7 @@ JIT keys N, K, BLOCK_M, BLOCK_N, NUM_STAGES) and adds the missing functions.  Th
 of CTAs one TMA load is delivered to, is fixed at 1: every CTA of this kernel loads its own tiles.
 By default a call goes to the prebuilt C-ABI library; `YAN_FP8_GEMM_JIT=1` routes it through
 `jit_tuner.compile_and_tune` with the template below, specialising N and K at compile time exactly
-as the reference intends.  Both run the same kernel source (include/gemm/fp8_gemm.cuh).
+as the reference intends (`YAN_FP8_GEMM_TUNE=1` additionally lets the tuner time every tile width).  Both run the same kernel source (include/gemm/fp8_gemm.cuh).
 """
 from __future__ import annotations
 
@@ -116,14 +116,20 @@ def gemm_fp8_fp8_bf16_nt(lhs: Tuple[torch.Tensor, torch.Tensor], rhs: Tuple[torc
     num_sms = get_num_sms()
     if int(os.environ.get("YAN_FP8_GEMM_JIT", "0")):
         from .tuner import jit_tuner
-        bn, stages, smem_size = get_best_configs(m, n, k, num_sms) if block_n == 0 else \
-            (block_n, _DEFAULT_STAGES[block_n], get_smem_size(block_n, _DEFAULT_STAGES[block_n]))
         assert out.stride(0) == n, "the JIT specialisation writes a dense [M, N] output"
-        args = (lhs_q, lhs_scales, rhs_q, rhs_scales, out, m, torch.cuda.current_stream(), num_sms, smem_size)
-        runtime = jit_tuner.compile_and_tune(
-            name='gemm_fp8_fp8_bf16_nt',
-            keys={'N': n, 'K': k, 'BLOCK_M': 128, 'BLOCK_N': bn, 'NUM_STAGES': stages},
-            space=(), includes=includes, arg_defs=arg_defs, template=template, args=args)
+        # smem_size = 0: each candidate checks its own requirement against the device limit and reports
+        # kSmemTooLarge through the return code, which the tuner treats as "skip this configuration".
+        args = (lhs_q, lhs_scales, rhs_q, rhs_scales, out, m, torch.cuda.current_stream(), num_sms, 0)
+        if block_n == 0 and int(os.environ.get("YAN_FP8_GEMM_TUNE", "0")):
+            # time every tile width that can fill the machine; the winner is remembered per (N, K, M bucket)
+            space = tuple({'BLOCK_N': bn, 'NUM_STAGES': _DEFAULT_STAGES[bn]} for bn in (256, 128, 64, 32) if bn <= n)
+            keys = {'N': n, 'K': k, 'BLOCK_M': 128, 'M_BUCKET': ceil_div(m, 128)}
+        else:
+            bn = get_best_configs(m, n, k, num_sms)[0] if block_n == 0 else block_n
+            space = ()
+            keys = {'N': n, 'K': k, 'BLOCK_M': 128, 'BLOCK_N': bn, 'NUM_STAGES': _DEFAULT_STAGES[bn]}
+        runtime = jit_tuner.compile_and_tune(name='gemm_fp8_fp8_bf16_nt', keys=keys, space=space, includes=includes,
+                                             arg_defs=arg_defs, template=template, args=args)
         rc = runtime(*args)
         if rc != 0:
             raise _lib.YanB200Error('gemm_fp8_fp8_bf16_nt[jit]', rc, 'see ReturnCode in include/gemm/utils.cuh')
