@@ -53,7 +53,9 @@ const char* yan_b200_return_code_string(int code);
  * describes: yan/jit_kernels/gemm.py:9-31 (`Gemm<...>::run(out, rhs_scales, nullptr, m, descs..., stream,
  * num_sms, smem_size)`) and the kernel yan/include/gemm/fp8_gemm.cuh:32-197.
  * block_n: 0 = choose, 32, 64, 128 or 256 = tile width of the general kernel, 1 = the weight-streaming kernel
- * for M <= 64 (YAN_B200_BAD_ARGUMENT when the problem does not fit it).  num_sms: CTAs of the persistent grid (<= device SMs).
+ * for M <= 64 (split-K over a pair of CTAs), 2 = the weight-streaming kernel for M <= 32 that keeps all of K in one
+ * CTA (YAN_B200_BAD_ARGUMENT when the problem does not fit the kernel asked for).
+ * num_sms: CTAs of the persistent grid (<= device SMs).
  */
 void yan_b200_gemm_fp8_fp8_bf16_nt(const void* lhs, const void* lhs_scales, const void* rhs, const void* rhs_scales,
                                    void* out, int m, int n, int k, int ldd, void* stream, int num_sms, int block_n,

@@ -93,6 +93,44 @@ def test_weight_streaming_kernel_limits(cuda_lib):
     assert _lib.call_rc(f, p, p, p, p, p, 64, 128, 8192, 128, stream, sms, 1) == 1   # too many k-blocks for TMEM
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 128, 512), (16, 7168, 2048), (9, 256, 1024), (16, 384, 4096), (17, 7168, 2048),
+                                   (32, 512, 2048), (5, 2048, 1536)])
+def test_stacked_k_kernel(cuda_lib, m, n, k):
+    """block_n=2 forces the stacked-K weight-streaming kernel (32 weight rows and all of K per CTA, the four
+    k-quarters on the four lane quarters of one MMA); compare with the oracle and with the general kernel."""
+    lhs, rhs = _operands(m, n, k, seed=m * 11 + k, outliers=True)
+    d_ref = ref.ref_gemm(lhs, rhs)
+    d_stacked = _run(lhs, rhs, block_n=2)
+    _check(d_stacked.cpu(), d_ref, f"stacked-K m={m} n={n} k={k}")
+    d_general = _run(lhs, rhs, block_n=64)
+    assert ref.rel_frobenius(d_stacked.cpu(), d_general.cpu()) <= 1e-3
+
+
+def test_stacked_k_kernel_partial_weight_block(cuda_lib):
+    """N = 96: three CTAs of 32 weight rows inside one 128-row scale block, output a slice of a wider buffer."""
+    lhs, rhs = _operands(12, 128, 1024, seed=5)
+    rhs96 = (rhs[0][:96].contiguous(), rhs[1])
+    full = torch.full((12, 256), 7.0, dtype=torch.bfloat16, device="cuda")
+    _run(lhs, rhs96, block_n=2, out=full[:, 64:160])
+    full = full.cpu()
+    _check(full[:, 64:160], ref.ref_gemm(lhs, rhs)[:, :96], "stacked-K slice")
+    assert bool((full[:, :64] == 7.0).all()) and bool((full[:, 160:] == 7.0).all())
+
+
+def test_stacked_k_kernel_limits(cuda_lib):
+    import ctypes
+    from yan_b200 import _lib
+    p = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda").data_ptr()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    f = "yan_b200_gemm_fp8_fp8_bf16_nt"
+    assert _lib.call_rc(f, p, p, p, p, p, 33, 128, 512, 128, stream, sms, 2) == 1    # M > 32
+    assert _lib.call_rc(f, p, p, p, p, p, 16, 144, 512, 144, stream, sms, 2) == 1    # N not a multiple of 32
+    assert _lib.call_rc(f, p, p, p, p, p, 16, 128, 768, 128, stream, sms, 2) == 1    # K not a multiple of 512
+    assert _lib.call_rc(f, p, p, p, p, p, 16, 128, 8192, 128, stream, sms, 2) == 1   # more than 8 steps
+    assert _lib.call_rc(f, p, p, p, p, p, 32, 128, 4096, 128, stream, sms, 2) == 1   # 8 steps x 128 TMEM columns
+
+
 def test_long_k_many_tiles(cuda_lib):
     """More tiles than SMs and a long K loop: exercises ring wrap-around and persistent scheduling."""
     lhs, rhs = _operands(1024, 2560, 4096, seed=3)

@@ -8,6 +8,7 @@
 #include "../../include/yan_b200.h"
 #include "gemm_dispatch.h"
 #include "gemm/fp8_gemm_small_m.cuh"
+#include "gemm/fp8_gemm_stacked_k.cuh"
 #include "quant/fp8_cast.cuh"
 
 namespace {
@@ -110,12 +111,24 @@ int dispatch_gemm(yan::GemmType type, yan::OutKind out_kind, yan::GemmArgs& a, i
     a.status = status_word_of_current_device();
     a.timeout_ns = g_timeout_ns;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // M <= 64: the weight-streaming kernel (block_n 1 asks for it explicitly, 0 lets it win when it fits).
-    if (type == yan::GemmType::Normal && out_kind == yan::OutKind::BF16 && (want_auto || block_n == 1)) {
+    // M <= 64: the weight-streaming kernels.  block_n 1 asks for the pair-cluster kernel, 2 for the stacked-K kernel
+    // (M <= 32), 0 picks the stacked one where it is the faster (M <= 16, two CTAs per SM), else the pair kernel.
+    if (type == yan::GemmType::Normal && out_kind == yan::OutKind::BF16 && (want_auto || block_n == 1 || block_n == 2)) {
         int dev = 0, max_smem = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
-        if (yan::small_m_supported(a.m, a.n, a.k, max_smem)) return yan::launch_fp8_gemm_small_m(a, s, g_programmatic_launch != 0 || after_own_quantizer);
+        const bool programmatic = g_programmatic_launch != 0 || after_own_quantizer;
+        if (block_n == 2) {
+            if (!yan::stacked_k_supported(a.m, a.n, a.k, max_smem)) return yan::kBadArgument;
+            return yan::launch_fp8_gemm_stacked_k(a, s, programmatic);
+        }
+        if (want_auto) {
+            int max_smem_sm = 0;
+            cudaDeviceGetAttribute(&max_smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
+            if (yan::stacked_k_preferred(a.m, a.n, a.k, max_smem, max_smem_sm))
+                return yan::launch_fp8_gemm_stacked_k(a, s, programmatic);
+        }
+        if (yan::small_m_supported(a.m, a.n, a.k, max_smem)) return yan::launch_fp8_gemm_small_m(a, s, programmatic);
         if (block_n == 1) return yan::kBadArgument;
     }
     switch (block_n) {

@@ -216,6 +216,11 @@ __device__ __forceinline__ void tmem_ld_wait<16>(uint32_t (&r)[16]) {
                  : "memory");
 }
 
+// bar.sync on a named barrier: the first `count` threads' worth of warps that reach it (count % 32 == 0).
+__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // register reallocation between warpgroups (same mechanism the reference uses at
 // fp8_gemm.cuh:171-181 through cutlass::arch::warpgroup_reg_alloc/dealloc)
