@@ -61,6 +61,16 @@ void yan_b200_gemm_fp8_fp8_bf16_nt(const void* lhs, const void* lhs_scales, cons
                                    void* out, int m, int n, int k, int ldd, void* stream, int num_sms, int block_n,
                                    int* return_code);
 
+/* Same GEMM with the next layer's quantizer fused into the epilogue: out = e4m3 [M, ldd] (ldd % 16 == 0, 16-byte
+ * aligned) and out_scales = fp32, k-block-major [N/128][out_scales_ld] (out_scales_ld >= m), i.e. exactly what
+ * yan_b200_per_token_cast_to_fp8 would produce from the bf16 output of yan_b200_gemm_fp8_fp8_bf16_nt (the accumulator is
+ * rounded to bf16, then quantized with the same three fp32 operations), bit for bit, without the bf16 tensor ever
+ * reaching memory.  N % 128 == 0.  No reference counterpart: the reference's epilogue writes bf16 only
+ * (yan/include/gemm/fp8_gemm.cuh:56,87). */
+void yan_b200_gemm_fp8_fp8_e4m3_nt(const void* lhs, const void* lhs_scales, const void* rhs, const void* rhs_scales,
+                                   void* out, void* out_scales, int m, int n, int k, int ldd, int out_scales_ld,
+                                   void* stream, int num_sms, int* return_code);
+
 /* Same GEMM with an fp32 output [M, ldd] (ldd % 4 == 0): the K-split path can then sum fp32 partials.
  * Takes the place of the fp32 partial tiles comm/gemm_allreduce.cu:57-60 reduces across ranks. */
 void yan_b200_gemm_fp8_fp8_f32_nt(const void* lhs, const void* lhs_scales, const void* rhs, const void* rhs_scales,

@@ -7,7 +7,8 @@ raises (no CPU or PyTorch fallback exists).
 """
 from . import jit
 from .jit_kernels import gemm
-from .jit_kernels import (ceil_div, fp8_linear, fp8_linear_workspace_bytes, gemm_fp8_fp8_bf16_nt, gemm_fp8_fp8_f32_nt,
+from .jit_kernels import (ceil_div, fp8_linear, fp8_linear_workspace_bytes, gemm_fp8_fp8_bf16_nt, gemm_fp8_fp8_e4m3_nt,
+                          gemm_fp8_fp8_f32_nt,
                           get_col_major_tensor, get_m_alignment_for_contiguous_layout, get_num_sms,
                           m_grouped_gemm_fp8_fp8_bf16_nt_contiguous, m_grouped_gemm_fp8_fp8_bf16_nt_masked,
                           per_block_cast_to_fp8, per_token_cast_to_fp8, read_device_status, set_num_sms,

@@ -26,6 +26,7 @@ SIGNATURES = {
     "yan_b200_return_code_string": (ctypes.c_char_p, [_I]),
     "yan_b200_gemm_fp8_fp8_bf16_nt": (None, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _RC]),
     "yan_b200_gemm_fp8_fp8_f32_nt": (None, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _RC]),
+    "yan_b200_gemm_fp8_fp8_e4m3_nt": (None, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _RC]),
     "yan_b200_m_grouped_gemm_fp8_fp8_bf16_nt_contiguous": (None, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _RC]),
     "yan_b200_m_grouped_gemm_fp8_fp8_bf16_nt_masked": (None, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _RC]),
     "yan_b200_per_token_cast_to_fp8": (None, [_P, _P, _P, _I, _I, _I, _I, _P, _RC]),

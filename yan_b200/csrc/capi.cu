@@ -217,6 +217,27 @@ YAN_EXPORT void yan_b200_gemm_fp8_fp8_f32_nt(const void* lhs, const void* lhs_sc
     set_rc(return_code, dispatch_gemm(yan::GemmType::Normal, yan::OutKind::F32, a, block_n, stream));
 }
 
+YAN_EXPORT void yan_b200_gemm_fp8_fp8_e4m3_nt(const void* lhs, const void* lhs_scales, const void* rhs,
+                                              const void* rhs_scales, void* out, void* out_scales, int m, int n, int k,
+                                              int ldd, int out_scales_ld, void* stream, int num_sms,
+                                              int* return_code) {
+    if (!positive(m, n, k) || ldd <= 0 || out_scales_ld <= 0) return set_rc(return_code, yan::kBadArgument);
+    yan::GemmArgs a;
+    a.lhs = lhs;
+    a.lhs_scales = static_cast<const float*>(lhs_scales);
+    a.lhs_scales_ld = static_cast<uint32_t>(m);
+    a.rhs = rhs;
+    a.rhs_scales = static_cast<const float*>(rhs_scales);
+    a.out = out;
+    a.ldd = static_cast<uint32_t>(ldd);
+    a.out_scales = static_cast<float*>(out_scales);
+    a.out_scales_ld = static_cast<uint32_t>(out_scales_ld);
+    a.m = m, a.n = n, a.k = k;
+    a.num_sms = num_sms;
+    // the epilogue quantizes one 1 x 128 group per thread, which only the 256-wide tile provides
+    set_rc(return_code, dispatch_gemm(yan::GemmType::Normal, yan::OutKind::E4M3, a, 256, stream));
+}
+
 YAN_EXPORT void yan_b200_m_grouped_gemm_fp8_fp8_bf16_nt_contiguous(const void* lhs, const void* lhs_scales,
                                                                    const void* rhs, const void* rhs_scales, void* out,
                                                                    const int* m_indices, int m, int n, int k,

@@ -7,7 +7,7 @@
 
 namespace yan {
 
-enum class OutKind { BF16 = 0, F32 = 1 };
+enum class OutKind { BF16 = 0, F32 = 1, E4M3 = 2 };
 
 int launch_gemm_bn32(GemmType type, OutKind out, const GemmArgs& args, cudaStream_t stream);
 int launch_gemm_bn64(GemmType type, OutKind out, const GemmArgs& args, cudaStream_t stream);

@@ -17,6 +17,15 @@ int YAN_CAT(launch_gemm_bn, YAN_BLOCK_N)(GemmType type, OutKind out, const GemmA
         if (type != GemmType::Normal) return kBadArgument;
         return GemmLauncher<BN, S, GemmType::Normal, float>::launch(args, stream);
     }
+    if (out == OutKind::E4M3) {
+        // one 1 x 128 quantization group per epilogue thread: only the 256-wide tile has it
+        if constexpr (BN == 256) {
+            if (type != GemmType::Normal) return kBadArgument;
+            return GemmLauncher<BN, S, GemmType::Normal, E4m3Out>::launch(args, stream);
+        } else {
+            return kBadArgument;
+        }
+    }
     switch (type) {
         case GemmType::Normal:
             return GemmLauncher<BN, S, GemmType::Normal, __nv_bfloat16>::launch(args, stream);

@@ -40,6 +40,8 @@ struct GemmParams {
     const float* scales_b;      // [groups][ceil(N/128)][K/128]
     const int* grouped_layout;  // Contiguous: [M] group per row (-1 = padding); Masked: [G] valid rows
     void* out;                  // [rows][ldd]
+    float* out_scales;          // e4m3 output only: [N/128][out_scales_ld], element (nb, row) at nb * out_scales_ld + row
+    uint32_t out_scales_ld;
     uint32_t sa_ld;
     uint32_t ldd;
     uint32_t shape_m;  // Normal/Contiguous: total rows; Masked: rows per group (M_max)
@@ -101,7 +103,42 @@ __device__ __forceinline__ void store_row(out_t* dst, const float (&acc)[kCols],
     }
 }
 
+// Epilogue of the e4m3 output (the next layer's activation operand): the thread holds one whole 1 x 128 group of its
+// row, so the per-token-group quantizer runs in registers.  The values are rounded to bf16 first and then quantized
+// with the quantizer's own three fp32 operations (amax_c = max(amax, 1e-4); inv = 448 / amax_c; q = e4m3_rne(x * inv);
+// scale = amax_c / 448), so that the result is bit-identical to the bf16 GEMM followed by per_token_cast_to_fp8.
+__device__ __forceinline__ void store_row_e4m3(uint8_t* dst, float* scale_dst, float (&acc)[128]) {
+    float amax = 0.0f;
+#pragma unroll
+    for (uint32_t j = 0; j < 128; ++j) {
+        acc[j] = __bfloat162float(__float2bfloat16_rn(acc[j]));
+        amax = fmaxf(amax, fabsf(acc[j]));
+    }
+    const float amax_c = fmaxf(amax, 1e-4f);
+    const float inv = __fdiv_rn(448.0f, amax_c);
+#pragma unroll
+    for (uint32_t j = 0; j < 8; ++j) {
+        uint32_t w[4];
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) {
+            const float* a = acc + j * 16 + i * 4;
+            const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(a[0], inv), __fmul_rn(a[1], inv)),
+                                                         __NV_SATFINITE, __NV_E4M3);
+            const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(a[2], inv), __fmul_rn(a[3], inv)),
+                                                         __NV_SATFINITE, __NV_E4M3);
+            w[i] = lo | (hi << 16);
+        }
+        *reinterpret_cast<uint4*>(dst + j * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    *scale_dst = __fdiv_rn(amax_c, 448.0f);
+}
+
 }  // namespace detail
+
+// Output element type of the quantized-output GEMM: e4m3 codes plus one fp32 scale per (row, 128 columns).
+struct E4m3Out {
+    uint8_t code;
+};
 
 template <uint32_t BLOCK_N, uint32_t kNumStages>
 struct GemmSmemLayout {
@@ -335,8 +372,16 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
                 }
             }
             if (alive && row_ok) {
-                out_t* dst = reinterpret_cast<out_t*>(p.out) + static_cast<size_t>(row) * p.ldd + n_first;
-                detail::store_row<out_t, kColsPerWG>(dst, acc, n_first, p.shape_n);
+                if constexpr (sizeof(out_t) == 1) {
+                    static_assert(kColsPerWG == 128, "the e4m3 output needs one 128-column group per thread: BLOCK_N = 256");
+                    if (n_first < p.shape_n)
+                        detail::store_row_e4m3(
+                            reinterpret_cast<uint8_t*>(p.out) + static_cast<size_t>(row) * p.ldd + n_first,
+                            p.out_scales + static_cast<size_t>(n_first / 128u) * p.out_scales_ld + row, acc);
+                } else {
+                    out_t* dst = reinterpret_cast<out_t*>(p.out) + static_cast<size_t>(row) * p.ldd + n_first;
+                    detail::store_row<out_t, kColsPerWG>(dst, acc, n_first, p.shape_n);
+                }
             }
         }
         __syncwarp();
@@ -363,6 +408,8 @@ struct GemmArgs {
     const float* rhs_scales = nullptr; // [groups, ceil(N/128), K/128]
     void* out = nullptr;               // [rows, ldd]
     uint32_t ldd = 0;
+    float* out_scales = nullptr;       // e4m3 output only: [N/128, out_scales_ld]
+    uint32_t out_scales_ld = 0;
     const int* grouped_layout = nullptr;
     uint32_t m = 0, n = 0, k = 0, num_groups = 1;
     int num_sms = 0;
@@ -387,6 +434,9 @@ struct GemmLauncher {
         if (a.ldd < a.n || a.ldd % kVec != 0 || a.lhs_scales_ld == 0) return kBadArgument;
         if (!is_aligned(a.lhs, 16) || !is_aligned(a.rhs, 16) || !is_aligned(a.out, 16) || !is_aligned(a.lhs_scales, 4) ||
             !is_aligned(a.rhs_scales, 4))
+            return kBadArgument;
+        if (sizeof(out_t) == 1 &&
+            (a.out_scales == nullptr || a.out_scales_ld < a.m || a.n % 128 != 0 || !is_aligned(a.out_scales, 4)))
             return kBadArgument;
         if (kGemmType != GemmType::Normal && a.grouped_layout == nullptr) return kBadArgument;
         if (kGemmType == GemmType::Normal && a.num_groups != 1) return kBadArgument;
@@ -416,6 +466,8 @@ struct GemmLauncher {
         p.scales_b = a.rhs_scales;
         p.grouped_layout = a.grouped_layout;
         p.out = a.out;
+        p.out_scales = a.out_scales;
+        p.out_scales_ld = a.out_scales_ld;
         p.sa_ld = a.lhs_scales_ld;
         p.ldd = a.ldd;
         p.shape_m = a.m;

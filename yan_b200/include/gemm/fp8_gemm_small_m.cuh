@@ -289,6 +289,8 @@ inline int launch_fp8_gemm_small_m(const GemmArgs& a, cudaStream_t stream, bool 
     p.scales_b = a.rhs_scales;
     p.grouped_layout = nullptr;
     p.out = a.out;
+    p.out_scales = nullptr;
+    p.out_scales_ld = 0;
     p.sa_ld = a.lhs_scales_ld;
     p.ldd = a.ldd;
     p.shape_m = a.m;

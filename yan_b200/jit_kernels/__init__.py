@@ -1,4 +1,4 @@
-from .gemm import (gemm_fp8_fp8_bf16_nt, gemm_fp8_fp8_f32_nt, m_grouped_gemm_fp8_fp8_bf16_nt_contiguous,
+from .gemm import (gemm_fp8_fp8_bf16_nt, gemm_fp8_fp8_e4m3_nt, gemm_fp8_fp8_f32_nt, m_grouped_gemm_fp8_fp8_bf16_nt_contiguous,
                    m_grouped_gemm_fp8_fp8_bf16_nt_masked, fp8_linear, fp8_linear_workspace_bytes, read_device_status,
                    set_programmatic_dependent_launch)
 from .quant import per_token_cast_to_fp8, per_block_cast_to_fp8

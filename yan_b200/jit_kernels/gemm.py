@@ -150,6 +150,35 @@ def gemm_fp8_fp8_f32_nt(lhs, rhs, out: torch.Tensor, block_n: int = 0) -> None:
               rhs_scales.data_ptr(), out.data_ptr(), m, n, k, out.stride(0), _stream_ptr(), get_num_sms(), block_n)
 
 
+def gemm_fp8_fp8_e4m3_nt(lhs, rhs, out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
+                         ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The GEMM with the next layer's activation quantizer fused into its epilogue.
+
+    Returns (e4m3 [M,N], fp32 scales [M, N/128] stored column-major) -- the `lhs` operand of the following
+    gemm_fp8_fp8_*_nt -- equal bit for bit to per_token_cast_to_fp8(bf16 output of gemm_fp8_fp8_bf16_nt(..., block_n=256)),
+    without the bf16 tensor being written or read.  N must be a multiple of 128.  The reference's epilogue writes
+    bf16 only (yan/include/gemm/fp8_gemm.cuh:56,87)."""
+    lhs_q, lhs_scales = lhs
+    rhs_q, rhs_scales = rhs
+    m, n = lhs_q.shape[0], rhs_q.shape[0]
+    assert n % 128 == 0, "the fused quantizer works on whole 1 x 128 groups"
+    if out is None:
+        out = (torch.empty((m, n), dtype=torch.float8_e4m3fn, device=lhs_q.device),
+               torch.empty((n // 128, m), dtype=torch.float32, device=lhs_q.device).t())
+    out_q, out_scales = out
+    m, n, k = _check_operands(lhs_q, lhs_scales, rhs_q, rhs_scales, out_q, torch.float8_e4m3fn)
+    assert out_scales.dtype == torch.float32 and out_scales.shape == (m, n // 128) and out_scales.is_cuda
+    assert out_scales.stride(0) == 1 and (n == 128 or out_scales.stride(1) >= m), "scales are stored column-major"
+    lhs_scales = get_col_major_tensor(lhs_scales)
+    if m == 1 or lhs_scales.stride(1) != m:
+        lhs_scales = lhs_scales.t().contiguous().t()
+    out_scales_ld = out_scales.stride(1) if n > 128 else m
+    _lib.call("yan_b200_gemm_fp8_fp8_e4m3_nt", lhs_q.data_ptr(), lhs_scales.data_ptr(), rhs_q.data_ptr(),
+              rhs_scales.data_ptr(), out_q.data_ptr(), out_scales.data_ptr(), m, n, k, out_q.stride(0), out_scales_ld,
+              _stream_ptr(), get_num_sms())
+    return out_q, out_scales
+
+
 def m_grouped_gemm_fp8_fp8_bf16_nt_contiguous(lhs, rhs, out: torch.Tensor, m_indices: torch.Tensor,
                                               block_n: int = 0) -> None:
     """Grouped GEMM, contiguous layout (yan/include/gemm/scheduler.cuh:9, GemmType::GroupedContiguous):
