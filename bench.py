@@ -262,6 +262,28 @@ def bench_dense(name: str, m: int, n: int, k: int, peaks, iters: int = 10) -> di
             "quant_frac_of_measured_hbm": qbytes / tq / 1e9 / peaks["hbm_gbs"]}
 
 
+def bench_fused_epilogue(m: int, n: int, k: int, iters: int = 10) -> dict:
+    """Layer i's GEMM followed by layer i+1's activation quantizer: two kernels through a bf16 tensor against the GEMM
+    whose epilogue writes e4m3 + scales directly (the outputs are bit-identical; tests/test_gemm_e4m3_out_gpu.py)."""
+    import yan_b200
+    from yan_b200.utils import bench_events
+    a, rhs = make_device_inputs(m, n, k, 0)
+    lhs = yan_b200.per_token_cast_to_fp8(a)
+    d = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    q = yan_b200.per_token_cast_to_fp8(d)
+    fused_out = yan_b200.gemm_fp8_fp8_e4m3_nt(lhs, rhs)
+
+    def two_kernels():
+        yan_b200.gemm_fp8_fp8_bf16_nt(lhs, rhs, d)
+        yan_b200.per_token_cast_to_fp8(d, out=q)
+
+    t2 = bench_events(two_kernels, num_tests=iters, flush_l2=True)
+    t1 = bench_events(lambda: yan_b200.gemm_fp8_fp8_e4m3_nt(lhs, rhs, out=fused_out), num_tests=iters, flush_l2=True)
+    return {"workload": f"GEMM + next layer's quantizer M={m} N={n} K={k}", "gemm_then_quantizer_us": t2 * 1e6,
+            "fused_epilogue_us": t1 * 1e6, "speedup": t2 / t1,
+            "hbm_bytes_saved": 2 * m * n + 2 * m * n}
+
+
 def bench_k_split(rank: int, world: int, dist, steps: int = 10) -> dict:
     """Row-parallel GEMM + allreduce (M=4096, N=8192, K=28672 split along K over the ranks): per step each rank
     quantizes its K shard of A, computes a full-size bf16 partial D in row chunks and sums the partials with an NCCL
@@ -486,6 +508,8 @@ def run_ours(args) -> None:
             extras.append(bench_decode(m_small, peaks))
         extras.append(bench_dense("C3 mid-size projection", 4096, 7168, 18432, peaks))
         extras.append(bench_dense("C1 CPU-runnable", 256, 1024, 1024, peaks))
+        extras.append(bench_fused_epilogue(4096, 7168, 18432))
+        extras.append(bench_fused_epilogue(8192, 7168, 2048))
         line["other_workloads"] = extras
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         a_cpu, rhs_cpu = make_cpu_inputs()

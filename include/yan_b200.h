@@ -161,6 +161,38 @@ void yan_b200_read_device_status(int* status, int reset, int* return_code);
 void yan_b200_wait_probe(unsigned long long timeout_ns, void* stream, int* return_code);
 
 /*
+ * Peer-mapped device memory inside one NVSwitch box (CUDA IPC), for the K-split GEMM's exchange step.  They stand in
+ * for the NVSHMEM symmetric heap of the reference (comm/gemm_allreduce.cu:238-259: nvshmem_malloc / nvshmem_ptr).
+ * yan_b200_ipc_export: handle (YAN_B200_IPC_HANDLE_BYTES bytes, to be sent to the other processes of the box) of the
+ *   allocation that contains `ptr`, and the offset of `ptr` inside it.  The memory must come from cudaMalloc (the
+ *   default allocator of PyTorch qualifies; its expandable segments do not).
+ * yan_b200_ipc_open: maps another process's allocation into this process (peer access is enabled on first use);
+ *   *base + offset is the peer's `ptr`.  yan_b200_ipc_close unmaps it.  None of the three touches a stream.
+ */
+#define YAN_B200_IPC_HANDLE_BYTES 64
+void yan_b200_ipc_export(const void* ptr, void* handle, unsigned long long* offset, int* return_code);
+void yan_b200_ipc_open(const void* handle, void** base, int* return_code);
+void yan_b200_ipc_close(void* base, int* return_code);
+
+/*
+ * In-place allreduce (sum) of bf16 elements [elem_begin, elem_begin + elem_count) of `world` same-shaped buffers,
+ * one per rank of the box: data[r] is rank r's buffer as seen from this process (data[rank] local, the others mapped
+ * with yan_b200_ipc_open).  Every rank calls it with the same range.  Rank r sums the r-th 1/world of the range in
+ * fp32 (rank order, one rounding) and stores the result into all buffers: plain peer loads and stores, no multimem.
+ * Replaces the per-tile NVLS reduction of comm/gemm_allreduce.cu:57-60,339-401.
+ * epoch != 0: signals[r] is rank r's zero-initialised 128-byte signal block (peer-mapped like data); the kernel waits
+ *   on entry until every rank has reached the same epoch and on exit until every rank's stores have landed.  epoch
+ *   must grow by one per call and counter_target must be the sum of num_ctas over all calls so far (this one
+ *   included), identically on every rank.  Waits are bounded (yan_b200_set_wait_timeout_ns) and report
+ *   (YAN_B200_DEVICE_TIMEOUT << 8) | 16 or 17 through the status word.
+ * epoch == 0: no device-side waiting; the caller orders the ranks before and after the call.
+ * elem_begin and elem_count are multiples of 8; 2 <= world <= 8; num_ctas > 0 (CTAs of 512 threads).
+ */
+void yan_b200_allreduce_bf16_two_shot(void* const* data, void* const* signals, int world, int rank,
+                                      unsigned long long elem_begin, unsigned long long elem_count, unsigned int epoch,
+                                      unsigned int counter_target, int num_ctas, void* stream, int* return_code);
+
+/*
  * Programmatic dependent launch for the weight-streaming (M <= 64) kernel.  When enabled, that kernel is
  * launched with cudaLaunchAttributeProgrammaticStreamSerialization: its weight loads (rhs) may start while the
  * previous kernel of the stream is still running; activations, scales of the activations and the output are

@@ -65,6 +65,28 @@ def _worker(rank: int, world: int, port: int, mode: str, results):
                                       partial_dtype=torch.bfloat16, gemm_fn=_oracle_gemm)
             d_split = ref.ref_gemm_k_split(lhs, rhs, world)
             ok = ref.rel_frobenius(out, d_split) <= 2e-3 and ref.rel_frobenius(out, d_ref) <= 6e-3
+        elif mode == "k_split_two_shot_host":
+            # the orchestration of the peer-memory path with a stand-in communicator: fp32 sum in rank order, one rounding
+            class HostComm:
+                def __init__(self):
+                    self.m, self.n = m, n
+                    self.buffer = torch.zeros(m, n, dtype=torch.bfloat16)
+                    self.calls = []
+
+                def reduce_rows(self, r0=0, r1=None, num_ctas=None):
+                    self.calls.append((r0, r1))
+                    parts = [torch.empty(r1 - r0, n) for _ in range(world)]
+                    dist.all_gather(parts, self.buffer[r0:r1].float())
+                    acc = torch.zeros(r1 - r0, n)
+                    for part in parts:
+                        acc += part
+                    self.buffer[r0:r1] = acc.to(torch.bfloat16)
+
+            comm = HostComm()
+            res = ga.gemm_k_split_two_shot(ga.shard_k(lhs, rank, world), ga.shard_k(rhs, rank, world), comm,
+                                           gemm_fn=_oracle_gemm)
+            ok = res is comm.buffer and comm.calls == [(0, m)]
+            ok = ok and ref.rel_frobenius(res, ref.ref_gemm_k_split(lhs, rhs, world)) <= 2e-3
         elif mode == "rank_failure":
             # A rank that raises before the collective: the survivor's allreduce must end with an error, not hang.
             if rank == 1:
@@ -100,7 +122,7 @@ def _run(mode: str, expect_all: bool = True):
     return dict(results), [p.exitcode for p in procs]
 
 
-@pytest.mark.parametrize("mode", ["n_split", "k_split_f32", "k_split_bf16"])
+@pytest.mark.parametrize("mode", ["n_split", "k_split_f32", "k_split_bf16", "k_split_two_shot_host"])
 def test_sharded_gemm_world2_gloo(mode):
     results, codes = _run(mode)
     assert codes == [0, 0], codes
@@ -123,3 +145,17 @@ def test_shard_helpers_reject_ragged_cuts():
         ga.shard_k((q, s), 0, 4)            # 256 / 4 = 64 columns: not whole k-blocks
     qs, ss = ga.shard_k((q, s), 1, 2)
     assert qs.shape == (384, 128) and ss.shape == (3, 1)
+
+
+def test_two_shot_slices_partition_the_range():
+    """Every 16-byte vector of the range is reduced by exactly one rank, for ranges that do not divide evenly too."""
+    from yan_b200.comm import slice_bounds
+    for world in range(2, 9):
+        for count in (1, 7, 8, 9, 1000, 4096 * 8192 // 8):
+            covered = []
+            for rank in range(world):
+                first, last = slice_bounds(count, world, rank)
+                assert 0 <= first <= last <= count
+                covered.append((first, last))
+            assert covered[0][0] == 0 and covered[-1][1] == count
+            assert all(covered[i][1] == covered[i + 1][0] for i in range(world - 1))

@@ -74,3 +74,77 @@ def test_n_split_and_k_split_over_nccl(cuda_lib):
         assert not p.is_alive(), "rank did not finish"
     assert [p.exitcode for p in procs] == [0, 0]
     assert dict(results) == {0: True, 1: True}
+
+
+def _two_shot_worker(rank, world, port, results):
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import yan_b200
+        from oracle import ref
+        from yan_b200.comm import TwoShotAllreduce, gemm_allreduce as ga
+        m, n, k = 512, 1024, 2048
+        ok = True
+        for device_barriers in (True, False):
+            comm = TwoShotAllreduce(m, n, device_barriers=device_barriers)
+            # 1. the collective alone: every rank can reproduce every rank's input from its seed
+            parts = []
+            for r in range(world):
+                g = torch.Generator(device="cuda").manual_seed(100 + r)
+                parts.append(torch.randn(m, n, generator=g, device="cuda").to(torch.bfloat16))
+            want = torch.zeros(m, n, device="cuda")
+            for part in parts:
+                want += part.float()
+            want = want.to(torch.bfloat16)
+            comm.buffer.copy_(parts[rank])
+            comm.reduce_rows()
+            torch.cuda.synchronize()
+            ok &= torch.equal(comm.buffer, want)
+            # 2. a row range only: the rows outside keep this rank's own values
+            comm.buffer.copy_(parts[rank])
+            comm.reduce_rows(128, 384, num_ctas=7)
+            torch.cuda.synchronize()
+            ok &= torch.equal(comm.buffer[128:384], want[128:384])
+            ok &= torch.equal(comm.buffer[:128], parts[rank][:128]) and torch.equal(comm.buffer[384:], parts[rank][384:])
+            # 3. the K-split GEMM on top of it, whole and in two overlapped row chunks
+            a, b = ref.make_inputs(m, n, k, seed=3)
+            lhs, rhs = ref.per_token_cast_to_fp8(a), ref.per_block_cast_to_fp8(b)
+            ks = k // world
+            lhs_local = yan_b200.per_token_cast_to_fp8(a[:, rank * ks:(rank + 1) * ks].contiguous().cuda())
+            rhs_k = tuple(t.contiguous().cuda() for t in ga.shard_k(rhs, rank, world))
+            d_split = ref.ref_gemm_k_split(lhs, rhs, world)
+            nccl = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+            ga.gemm_k_split_allreduce(lhs_local, rhs_k, nccl, partial_dtype=torch.bfloat16)
+            for chunks in (1, 2):
+                out = ga.gemm_k_split_two_shot(lhs_local, rhs_k, comm, num_chunks=chunks)
+                torch.cuda.synchronize()
+                ok &= ref.rel_frobenius(out.cpu(), d_split) <= 2e-3
+                if world == 2:  # the sum of two bf16 numbers rounded once: the same whoever adds them
+                    ok &= torch.equal(out, nccl)
+            ok &= yan_b200.read_device_status() == 0
+            comm.close()
+        results[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_shot_peer_allreduce_and_k_split(cuda_lib):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    ctx = mp.get_context("spawn")
+    results = ctx.Manager().dict()
+    port = _free_port()
+    os.environ.update(NCCL_NVLS_ENABLE="0")
+    procs = [ctx.Process(target=_two_shot_worker, args=(r, world, port, results)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(240)
+        assert not p.is_alive(), "rank did not finish"
+    assert [p.exitcode for p in procs] == [0, 0]
+    assert dict(results) == {0: True, 1: True}

@@ -31,6 +31,12 @@ SIGNATURES = {
     "yan_b200_m_grouped_gemm_fp8_fp8_bf16_nt_masked": (None, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _RC]),
     "yan_b200_per_token_cast_to_fp8": (None, [_P, _P, _P, _I, _I, _I, _I, _P, _RC]),
     "yan_b200_per_block_cast_to_fp8": (None, [_P, _P, _P, _I, _I, _P, _RC]),
+    "yan_b200_ipc_export": (None, [_P, _P, ctypes.POINTER(ctypes.c_ulonglong), _RC]),
+    "yan_b200_ipc_open": (None, [_P, ctypes.POINTER(ctypes.c_void_p), _RC]),
+    "yan_b200_ipc_close": (None, [_P, _RC]),
+    "yan_b200_allreduce_bf16_two_shot": (None, [ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p), _I, _I,
+                                                ctypes.c_ulonglong, ctypes.c_ulonglong, ctypes.c_uint, ctypes.c_uint, _I,
+                                                _P, _RC]),
     "yan_b200_fp8_linear_workspace_bytes": (ctypes.c_size_t, [_I, _I]),
     "yan_b200_fp8_linear_bf16": (None, [_P, _P, _P, _P, _P, ctypes.c_size_t, _I, _I, _I, _I, _P, _I, _I, _RC]),
     "yan_b200_fp8_linear_bf16_static": (None, [_P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _RC]),

@@ -10,7 +10,11 @@ into a CUTLASS fp16 GEMM epilogue (row-parallel: every PE computes a full-size p
   and the partials are summed with an allreduce over NCCL (NVLink 5 / NVSwitch).  The rows are processed in
   chunks so that the allreduce of chunk i runs on a second stream while the GEMM of chunk i+1 computes.
 
-Nothing remote is read by a kernel of this package: remote data reaches local HBM through the collective.
+* K-split with the two-shot peer-memory allreduce (`gemm_k_split_two_shot`): the GEMM writes its partial into a
+  buffer the other ranks have mapped (peer_memory.TwoShotAllreduce) and one kernel per rank sums the ranks' buffers in
+  place with plain peer loads and stores -- no NCCL call on the data path.
+
+The GEMM itself never reads remote memory; TMA and MMA operands are always local.
 `gemm_fn` lets host-side tests substitute the arithmetic; the default is the CUDA GEMM.
 """
 from __future__ import annotations
@@ -116,3 +120,49 @@ def gemm_k_split_allreduce(lhs_shard: Operand, rhs_shard: Operand, out: torch.Te
         for ev in done:
             main.wait_event(ev)
     return out
+
+
+def gemm_k_split_two_shot(lhs_shard: Operand, rhs_shard: Operand, comm, num_chunks: int = 1, comm_sms: int = 16,
+                          gemm_fn: Optional[Callable] = None,
+                          comm_stream: Optional["torch.cuda.Stream"] = None) -> torch.Tensor:
+    """K-split GEMM whose partials are summed by the two-shot peer-memory kernel instead of NCCL.
+
+    `comm` is a peer_memory.TwoShotAllreduce for [M, N]; the GEMM writes its bf16 partial straight into `comm.buffer`
+    (peer-mapped memory), the kernel sums the ranks' buffers in place (fp32 sum, one rounding) and the result is
+    returned in `comm.buffer` on every rank.  With num_chunks > 1 the rows go in chunks of whole 128-row tiles: the
+    GEMM of chunk i+1 runs on all but `comm_sms` SMs while the allreduce of chunk i uses those on a second stream.
+    Calls may follow one another on the same stream: a rank's allreduce kernel stores nothing before every rank has
+    entered the same call, which each rank does only after its own earlier work on the buffer (stream order)."""
+    from ..jit_kernels.utils import get_num_sms, set_num_sms
+    m, n = comm.m, comm.n
+    assert lhs_shard[0].shape[0] == m and rhs_shard[0].shape[0] == n
+    gemm = gemm_fn or _default_gemm(torch.bfloat16)
+    buf = comm.buffer
+    qa, sa = lhs_shard
+    if num_chunks <= 1:
+        gemm(lhs_shard, rhs_shard, buf)
+        comm.reduce_rows(0, m)
+        return buf
+    rows_per_chunk = max(128, -(-m // num_chunks) // 128 * 128)
+    bounds = [(r0, min(m, r0 + rows_per_chunk)) for r0 in range(0, m, rows_per_chunk)]
+    comm_stream = comm_stream or torch.cuda.Stream(device=buf.device)
+    main = torch.cuda.current_stream(buf.device)
+    all_sms = get_num_sms()
+    sm_threads = 2048 // 512  # CTAs of the allreduce kernel one SM can hold
+    try:
+        for i, (r0, r1) in enumerate(bounds):
+            # the first chunk has the GPU to itself; later ones share it with the allreduce of the chunk before
+            set_num_sms(all_sms if i == 0 else max(1, all_sms - comm_sms))
+            gemm((qa[r0:r1], sa[r0:r1]), rhs_shard, buf[r0:r1])
+            ready = torch.cuda.Event()
+            ready.record(main)
+            with torch.cuda.stream(comm_stream):
+                comm_stream.wait_event(ready)
+                last = i + 1 == len(bounds)
+                comm.reduce_rows(r0, r1, num_ctas=None if last else comm_sms * sm_threads)
+    finally:
+        set_num_sms(all_sms)
+    done = torch.cuda.Event()
+    done.record(comm_stream)
+    main.wait_event(done)
+    return buf

@@ -1,0 +1,129 @@
+"""Peer-mapped device memory and the two-shot allreduce kernel for the ranks of one NVSwitch box.
+
+The reference keeps its partial tiles in an NVSHMEM symmetric heap and reduces them with NVLS multimem loads inside
+the GEMM epilogue (comm/gemm_allreduce.cu:57-60,238-259,339-401).  This module gets the same effect -- a buffer every
+rank of the box can load from and store to -- with CUDA IPC handles exchanged through the process group, and sums the
+K-split partials with one kernel per rank over plain peer pointers (include/comm/peer_allreduce.cuh).
+One process per GPU; all ranks must be on the same machine.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import _lib
+
+SIGNAL_BYTES = 128  # one PeerSignals block (include/comm/peer_allreduce.cuh)
+
+# (pid of the exporter, handle bytes) -> [mapped base address, reference count]: an allocation is mapped once per process
+_opened: Dict[Tuple[int, bytes], List[int]] = {}
+
+
+def slice_bounds(count: int, world: int, rank: int) -> Tuple[int, int]:
+    """The part of `count` 16-byte vectors that `rank` reduces: ceil(count/world) vectors from rank*ceil(count/world),
+    clipped to the range (the last ranks of a short range may own nothing).  Mirrors the kernel's arithmetic."""
+    per = -(-count // world)
+    first = min(count, rank * per)
+    return first, min(count, first + per)
+
+
+class PeerSharedTensor:
+    """`local` is this rank's tensor; `ptrs[r]` is the address of rank r's tensor in this process."""
+
+    def __init__(self, shape, dtype: torch.dtype, group: Optional[dist.ProcessGroup] = None):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.local = torch.zeros(shape, dtype=dtype, device="cuda")
+        handle = (ctypes.c_ubyte * 64)()
+        offset = ctypes.c_ulonglong(0)
+        _lib.call("yan_b200_ipc_export", ctypes.c_void_p(self.local.data_ptr()), handle, ctypes.byref(offset))
+        mine = (os.getpid(), bytes(handle), int(offset.value), self.local.device.index)
+        everyone: list = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=group)
+        self._keys: List[Tuple[int, bytes]] = []
+        self.ptrs: List[int] = []
+        for r, (pid, h, off, _dev) in enumerate(everyone):
+            if r == self.rank:
+                self.ptrs.append(self.local.data_ptr())
+                continue
+            key = (pid, h)
+            if key not in _opened:
+                base = ctypes.c_void_p(0)
+                buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                _lib.call("yan_b200_ipc_open", buf, ctypes.byref(base))
+                _opened[key] = [int(base.value), 0]
+            _opened[key][1] += 1
+            self._keys.append(key)
+            self.ptrs.append(_opened[key][0] + off)
+        torch.cuda.synchronize()
+        dist.barrier(group=group)  # every rank has mapped every buffer (and zeroed its own) before anyone uses them
+
+    def ptr_array(self):
+        return (ctypes.c_void_p * self.world)(*self.ptrs)
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers.  Collective: no rank may still be using this rank's buffer."""
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        for key in self._keys:
+            entry = _opened[key]
+            entry[1] -= 1
+            if entry[1] == 0:
+                _lib.call("yan_b200_ipc_close", ctypes.c_void_p(entry[0]))
+                del _opened[key]
+        self._keys = []
+
+
+class TwoShotAllreduce:
+    """In-place sum over the ranks of a peer-shared bf16 matrix [M, N] (`buffer`): the GEMM writes its partial product
+    into `buffer`, `reduce_rows` leaves the sum of all ranks' partials there on every rank.
+
+    device_barriers=True : the kernel orders the ranks itself with epoch flags in peer memory (bounded waits).
+    device_barriers=False: the ranks are ordered by a one-element NCCL allreduce before and after the kernel.
+    """
+
+    def __init__(self, m: int, n: int, group: Optional[dist.ProcessGroup] = None, device_barriers: bool = True,
+                 num_ctas: Optional[int] = None):
+        assert n % 8 == 0, "rows are moved in 16-byte vectors"
+        self.group = group
+        self.m, self.n = m, n
+        # one allocation: the matrix, then the signal block
+        self._arena = PeerSharedTensor((m * n * 2 + SIGNAL_BYTES,), torch.uint8, group)
+        self.rank, self.world = self._arena.rank, self._arena.world
+        assert 2 <= self.world <= 8
+        self.buffer = self._arena.local[: m * n * 2].view(torch.bfloat16).view(m, n)
+        self._data = self._arena.ptr_array()
+        self._signals = (ctypes.c_void_p * self.world)(*[p + m * n * 2 for p in self._arena.ptrs])
+        self.device_barriers = device_barriers
+        sms = torch.cuda.get_device_properties(self.buffer.device).multi_processor_count
+        self.num_ctas = num_ctas or 2 * sms
+        self._epoch = 0
+        self._cta_count = 0
+        self._token = torch.zeros(1, dtype=torch.float32, device="cuda")
+
+    def reduce_rows(self, row_begin: int = 0, row_end: Optional[int] = None, num_ctas: Optional[int] = None) -> None:
+        """Allreduce of rows [row_begin, row_end) on the current stream.  Every rank makes the same calls in the same
+        order."""
+        row_end = self.m if row_end is None else row_end
+        assert 0 <= row_begin < row_end <= self.m
+        ctas = num_ctas or self.num_ctas
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        begin, count = row_begin * self.n, (row_end - row_begin) * self.n
+        if self.device_barriers:
+            self._epoch += 1
+            self._cta_count = (self._cta_count + ctas) & 0xFFFFFFFF
+            _lib.call("yan_b200_allreduce_bf16_two_shot", self._data, self._signals, self.world, self.rank, begin, count,
+                      self._epoch, self._cta_count, ctas, stream)
+        else:
+            dist.all_reduce(self._token, group=self.group)  # every rank's partial is complete
+            _lib.call("yan_b200_allreduce_bf16_two_shot", self._data, None, self.world, self.rank, begin, count, 0, 0,
+                      ctas, stream)
+            dist.all_reduce(self._token, group=self.group)  # every rank's stores have landed
+
+    def close(self) -> None:
+        self._arena.close()

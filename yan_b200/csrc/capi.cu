@@ -3,12 +3,15 @@
 // `return_code`; nothing allocates, frees or synchronises (except the explicit status read).
 
 #include <cstdint>
+#include <cstring>
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include "../../include/yan_b200.h"
 #include "gemm_dispatch.h"
 #include "gemm/fp8_gemm_small_m.cuh"
 #include "gemm/fp8_gemm_stacked_k.cuh"
+#include "comm/peer_allreduce.cuh"
 #include "quant/fp8_cast.cuh"
 
 namespace {
@@ -358,6 +361,79 @@ YAN_EXPORT void yan_b200_wait_probe(unsigned long long timeout_ns, void* stream,
     if (p.timeout_ns > 1000000000ull) return set_rc(return_code, yan::kBadArgument);  // a probe waits at most 1 s
     wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
     set_rc(return_code, cudaGetLastError() == cudaSuccess ? yan::kOk : yan::kLaunchFailed);
+}
+
+// ---- peer-mapped memory and the two-shot allreduce of the K-split GEMM ----
+
+YAN_EXPORT void yan_b200_ipc_export(const void* ptr, void* handle, unsigned long long* offset, int* return_code) {
+    if (ptr == nullptr || handle == nullptr || offset == nullptr) return set_rc(return_code, yan::kBadArgument);
+    static_assert(sizeof(cudaIpcMemHandle_t) == YAN_B200_IPC_HANDLE_BYTES, "handle size is part of the ABI");
+    using RangeFn = CUresult (*)(CUdeviceptr*, size_t*, CUdeviceptr);
+    static RangeFn range = []() -> RangeFn {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<RangeFn>(p);
+    }();
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    if (range == nullptr || range(&base, &size, reinterpret_cast<CUdeviceptr>(ptr)) != CUDA_SUCCESS)
+        return set_rc(return_code, yan::kCommFailed);
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base)) != cudaSuccess) {
+        cudaGetLastError();
+        return set_rc(return_code, yan::kCommFailed);
+    }
+    memcpy(handle, &h, sizeof(h));
+    *offset = static_cast<unsigned long long>(reinterpret_cast<CUdeviceptr>(ptr) - base);
+    set_rc(return_code, yan::kOk);
+}
+
+YAN_EXPORT void yan_b200_ipc_open(const void* handle, void** base, int* return_code) {
+    if (handle == nullptr || base == nullptr) return set_rc(return_code, yan::kBadArgument);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* p = nullptr;
+    if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        cudaGetLastError();
+        return set_rc(return_code, yan::kCommFailed);
+    }
+    *base = p;
+    set_rc(return_code, yan::kOk);
+}
+
+YAN_EXPORT void yan_b200_ipc_close(void* base, int* return_code) {
+    if (base == nullptr) return set_rc(return_code, yan::kBadArgument);
+    if (cudaIpcCloseMemHandle(base) != cudaSuccess) {
+        cudaGetLastError();
+        return set_rc(return_code, yan::kCommFailed);
+    }
+    set_rc(return_code, yan::kOk);
+}
+
+YAN_EXPORT void yan_b200_allreduce_bf16_two_shot(void* const* data, void* const* signals, int world, int rank,
+                                                 unsigned long long elem_begin, unsigned long long elem_count,
+                                                 unsigned int epoch, unsigned int counter_target, int num_ctas,
+                                                 void* stream, int* return_code) {
+    if (data == nullptr || world < 2 || world > yan::kMaxPeers || (epoch != 0 && signals == nullptr))
+        return set_rc(return_code, yan::kBadArgument);
+    yan::AllreduceArgs a;
+    for (int r = 0; r < world; ++r) {
+        a.data.p[r] = data[r];
+        a.signals.p[r] = (epoch != 0) ? signals[r] : nullptr;
+    }
+    a.world = world;
+    a.rank = rank;
+    a.elem_begin = elem_begin;
+    a.elem_count = elem_count;
+    a.epoch = epoch;
+    a.counter_target = counter_target;
+    a.num_ctas = num_ctas;
+    a.status = status_word_of_current_device();
+    a.timeout_ns = g_timeout_ns;
+    set_rc(return_code, yan::launch_two_shot_allreduce_bf16(a, static_cast<cudaStream_t>(stream)));
 }
 
 YAN_EXPORT void yan_b200_set_programmatic_dependent_launch(int enabled) { g_programmatic_launch = enabled; }

@@ -1,0 +1,198 @@
+#pragma once
+// Two-shot allreduce of a bf16 tensor over peer-mapped memory inside one NVSwitch box: the exchange step of the
+// K-split (row-parallel) GEMM, in place on the buffer the GEMM wrote its partial product to.
+//
+// The reference sums per-tile partials inside its GEMM epilogue through an NVSHMEM symmetric heap and NVLS multimem
+// instructions (comm/gemm_allreduce.cu:57-60,339-401).  Here every rank's buffer is ordinary device memory that the
+// other ranks of the box have mapped (CUDA IPC), and one kernel per rank does both halves of the collective:
+//   reduce-scatter: rank r owns the r-th 1/W of the range; it loads that slice from all W buffers (coalesced 16-byte
+//                   peer loads, all W in flight per thread), sums in fp32 in rank order and rounds to bf16 once;
+//   all-gather    : it stores the result to the same slice of all W buffers.
+// Inbound (loads) and outbound (stores) traffic run at the same time, NVLink being full duplex; per GPU
+// (W-1)/W of the tensor crosses each direction once, the minimum for an allreduce without in-switch reduction.
+// Plain ld/st on peer pointers only (no multimem, no bulk copies).
+//
+// Ordering between ranks, with epoch > 0, is part of the kernel: on entry a rank tells every peer that its partial
+// is complete (st.release.sys of the epoch into the peer's `arrive` slot) and waits until all peers said so; on exit,
+// after a system-scope fence, the last CTA tells every peer that its stores are done and waits for the same from
+// all, so completion of the kernel on one rank means the whole tensor is final there.  Every wait is bounded by a
+// wall-clock limit and reports through the status word; no CTA waits for another CTA of its own grid, so the kernel
+// finishes whatever part of the GPU it is given.  With epoch == 0 the caller provides both barriers (e.g. with a
+// collective of its communication library).
+
+#include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "../gemm/utils.cuh"
+
+namespace yan {
+
+constexpr int kMaxPeers = 8;
+
+struct PeerPtrs {
+    void* p[kMaxPeers];
+};
+
+// Layout of one rank's signal block (peer-mapped like the data; zero before first use).
+struct PeerSignals {
+    uint32_t arrive[kMaxPeers];  // arrive[r] = last epoch for which rank r's input is complete
+    uint32_t done[kMaxPeers];    // done[r]   = last epoch for which rank r's stores are complete
+    uint32_t cta_counter;        // CTAs of this rank that finished their stores, cumulative over launches
+    uint32_t pad[15];
+};
+
+namespace comm_detail {
+
+__device__ __forceinline__ uint64_t timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* addr, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 ld_sys_v4(const uint4* addr) {
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(addr)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ void fence_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+
+// Wait until *flag (local memory, written by a peer) has reached `epoch`.  Epochs only grow; the comparison is
+// wrap-safe.  Returns false after timeout_ns.
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, unsigned long long timeout_ns) {
+    const uint64_t t0 = timer_ns();
+    uint32_t spins = 0;
+    while (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) < 0) {
+        if ((++spins & 0xFu) == 0 && timer_ns() - t0 > timeout_ns) return false;
+    }
+    return true;
+}
+
+__device__ __forceinline__ void accumulate(float (&acc)[8], const uint4& v) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        acc[2 * i] += f.x;
+        acc[2 * i + 1] += f.y;
+    }
+}
+
+}  // namespace comm_detail
+
+// vec_begin / vec_count: the range to reduce, in 16-byte vectors (8 bf16) from the start of every buffer.
+template <int W>
+__global__ void __launch_bounds__(512)
+    two_shot_allreduce_bf16_kernel(const PeerPtrs data, const PeerPtrs signals, const int rank, const size_t vec_begin,
+                                   const size_t vec_count, const uint32_t epoch, const uint32_t counter_target,
+                                   int* status, const unsigned long long timeout_ns) {
+    static_assert(W >= 2 && W <= kMaxPeers, "one NVSwitch box");
+    __shared__ int s_ok;
+    PeerSignals* my_signals = static_cast<PeerSignals*>(signals.p[rank]);
+
+    // ---- entry: every rank's partial must be complete before anything is loaded ----
+    if (epoch != 0) {
+        if (threadIdx.x == 0) s_ok = 1;
+        __syncthreads();
+        if (blockIdx.x == 0 && threadIdx.x < W)
+            comm_detail::st_release_sys(&static_cast<PeerSignals*>(signals.p[threadIdx.x])->arrive[rank], epoch);
+        if (threadIdx.x < W && !comm_detail::wait_flag(&my_signals->arrive[threadIdx.x], epoch, timeout_ns)) {
+            s_ok = 0;
+            if (status != nullptr) atomicCAS(status, 0, (static_cast<int>(kDeviceTimeout) << 8) | 16);
+        }
+        __syncthreads();
+        if (s_ok == 0) return;  // inputs incomplete: leave the buffers alone (the host reads the status word)
+    }
+
+    // ---- this rank's slice: loads from all W buffers, one fp32 sum in rank order, stores to all W buffers ----
+    const size_t per_rank = (vec_count + W - 1) / W;
+    const size_t first = vec_begin + static_cast<size_t>(rank) * per_rank;
+    const size_t last = (first + per_rank < vec_begin + vec_count) ? first + per_rank : vec_begin + vec_count;
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = first + static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < last; i += stride) {
+        uint4 v[W];
+#pragma unroll
+        for (int r = 0; r < W; ++r) v[r] = comm_detail::ld_sys_v4(static_cast<const uint4*>(data.p[r]) + i);
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < W; ++r) comm_detail::accumulate(acc, v[r]);
+        uint4 o;
+        __nv_bfloat162 t;
+        t = __floats2bfloat162_rn(acc[0], acc[1]); o.x = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2bfloat162_rn(acc[2], acc[3]); o.y = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2bfloat162_rn(acc[4], acc[5]); o.z = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2bfloat162_rn(acc[6], acc[7]); o.w = *reinterpret_cast<uint32_t*>(&t);
+#pragma unroll
+        for (int r = 0; r < W; ++r) {
+            const int peer = (rank + r) % W;  // spread the ranks over the destinations at any instant
+            static_cast<uint4*>(data.p[peer])[i] = o;
+        }
+    }
+
+    // ---- exit: all ranks' stores must have landed before this kernel may complete ----
+    if (epoch != 0) {
+        comm_detail::fence_sys();
+        __syncthreads();
+        __shared__ int s_last;
+        if (threadIdx.x == 0) s_last = (atomicAdd(&my_signals->cta_counter, 1u) + 1u == counter_target);
+        __syncthreads();
+        if (s_last) {
+            if (threadIdx.x < W) {
+                comm_detail::fence_sys();
+                comm_detail::st_release_sys(&static_cast<PeerSignals*>(signals.p[threadIdx.x])->done[rank], epoch);
+                if (!comm_detail::wait_flag(&my_signals->done[threadIdx.x], epoch, timeout_ns) && status != nullptr)
+                    atomicCAS(status, 0, (static_cast<int>(kDeviceTimeout) << 8) | 17);
+            }
+        }
+    }
+}
+
+struct AllreduceArgs {
+    PeerPtrs data{};     // the same-shaped bf16 buffer on every rank; entry [rank] is local, the others peer-mapped
+    PeerPtrs signals{};  // PeerSignals blocks, same convention; unused when epoch == 0
+    int world = 0, rank = 0;
+    size_t elem_begin = 0, elem_count = 0;  // range in bf16 elements, both multiples of 8
+    uint32_t epoch = 0;                     // 0: the caller orders the ranks; otherwise a per-launch growing number
+    uint32_t counter_target = 0;            // sum of the grid sizes of all launches so far on this rank, this one included
+    int num_ctas = 0;                       // grid size (> 0)
+    int* status = nullptr;
+    unsigned long long timeout_ns = 2000000000ull;
+};
+
+inline int launch_two_shot_allreduce_bf16(const AllreduceArgs& a, cudaStream_t stream) {
+    if (a.world < 2 || a.world > kMaxPeers || a.rank < 0 || a.rank >= a.world || a.num_ctas <= 0) return kBadArgument;
+    if (a.elem_begin % 8 != 0 || a.elem_count % 8 != 0 || a.elem_count == 0) return kBadArgument;
+    for (int r = 0; r < a.world; ++r) {
+        if (a.data.p[r] == nullptr || reinterpret_cast<uintptr_t>(a.data.p[r]) % 16 != 0) return kBadArgument;
+        if (a.epoch != 0 && (a.signals.p[r] == nullptr || reinterpret_cast<uintptr_t>(a.signals.p[r]) % 4 != 0))
+            return kBadArgument;
+    }
+    const size_t vb = a.elem_begin / 8, vc = a.elem_count / 8;
+    const dim3 grid(static_cast<unsigned>(a.num_ctas)), block(512);
+#define YAN_LAUNCH_TWO_SHOT(W)                                                                                   \
+    two_shot_allreduce_bf16_kernel<W><<<grid, block, 0, stream>>>(a.data, a.signals, a.rank, vb, vc, a.epoch,    \
+                                                                  a.counter_target, a.status, a.timeout_ns)
+    switch (a.world) {
+        case 2: YAN_LAUNCH_TWO_SHOT(2); break;
+        case 3: YAN_LAUNCH_TWO_SHOT(3); break;
+        case 4: YAN_LAUNCH_TWO_SHOT(4); break;
+        case 5: YAN_LAUNCH_TWO_SHOT(5); break;
+        case 6: YAN_LAUNCH_TWO_SHOT(6); break;
+        case 7: YAN_LAUNCH_TWO_SHOT(7); break;
+        default: YAN_LAUNCH_TWO_SHOT(8); break;
+    }
+#undef YAN_LAUNCH_TWO_SHOT
+    return cudaGetLastError() == cudaSuccess ? kOk : kCommFailed;
+}
+
+}  // namespace yan
