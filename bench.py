@@ -284,6 +284,25 @@ def bench_fused_epilogue(m: int, n: int, k: int, iters: int = 10) -> dict:
             "hbm_bytes_saved": 2 * m * n + 2 * m * n}
 
 
+def _time_k_split(step, dist, steps: int, m: int, n: int, k: int, flops: bool = True) -> dict:
+    for _ in range(3):
+        step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if not flops:
+        return {"ms": t.item()}
+    return {"ms_per_step": t.item(), "TFLOP/s": 2.0 * m * n * k / (t.item() / 1e3) / 1e12}
+
+
 def bench_k_split(rank: int, world: int, dist, steps: int = 10) -> dict:
     """Row-parallel GEMM + allreduce (M=4096, N=8192, K=28672 split along K over the ranks): per step each rank
     quantizes its K shard of A, computes a full-size bf16 partial D in row chunks and sums the partials with an NCCL
@@ -302,25 +321,39 @@ def bench_k_split(rank: int, world: int, dist, steps: int = 10) -> dict:
     out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
     comm_stream = torch.cuda.Stream()
     results = {}
-    for label, chunks in (("single allreduce", 1), ("4 row chunks overlapped", 4)):
+    for label, chunks in (("NCCL, single allreduce", 1), ("NCCL, 4 row chunks overlapped", 4)):
         def step():
             yan_b200.per_token_cast_to_fp8(a, out=lhs)
             ga.gemm_k_split_allreduce(lhs, rhs, out, partial_dtype=torch.bfloat16, num_chunks=chunks, comm_stream=comm_stream)
-        for _ in range(3):
-            step()
-        dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            step()
-        e1.record()
-        dist.barrier()
-        torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        results[label] = {"ms_per_step": t.item(), "TFLOP/s": 2.0 * m * n * k / (t.item() / 1e3) / 1e12}
-    return {"workload": f"C5 row-parallel GEMM + allreduce M={m} N={n} K={k} (K/{world} per GPU, bf16 partials, NCCL)",
+        results[label] = _time_k_split(step, dist, steps, m, n, k)
+    # The same step with the partials summed by this package's two-shot kernel over peer-mapped memory (the GEMM writes
+    # straight into the shared buffer), and the two collectives alone on the same 64 MiB tensor.
+    try:
+        from yan_b200.comm import TwoShotAllreduce
+        comm = TwoShotAllreduce(m, n)
+        for label, chunks in (("two-shot peer allreduce", 1), ("two-shot peer allreduce, 4 row chunks overlapped", 4)):
+            def step():
+                yan_b200.per_token_cast_to_fp8(a, out=lhs)
+                ga.gemm_k_split_two_shot(lhs, rhs, comm, num_chunks=chunks, comm_stream=comm_stream)
+            results[label] = _time_k_split(step, dist, steps, m, n, k)
+        try:
+            comm_sw = TwoShotAllreduce(m, n, in_switch=True)
+            for label, chunks in (("in-switch peer allreduce", 1), ("in-switch peer allreduce, 4 row chunks overlapped", 4)):
+                def step():
+                    yan_b200.per_token_cast_to_fp8(a, out=lhs)
+                    ga.gemm_k_split_two_shot(lhs, rhs, comm_sw, num_chunks=chunks, comm_stream=comm_stream)
+                results[label] = _time_k_split(step, dist, steps, m, n, k)
+            results["allreduce alone, in-switch"] = _time_k_split(lambda: comm_sw.reduce_rows(), dist, steps, m, n, k, flops=False)
+            comm_sw.close()
+        except Exception as e:
+            results["in-switch peer allreduce"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+        results["allreduce alone, NCCL"] = _time_k_split(lambda: dist.all_reduce(out), dist, steps, m, n, k, flops=False)
+        results["allreduce alone, two-shot"] = _time_k_split(lambda: comm.reduce_rows(), dist, steps, m, n, k, flops=False)
+        results["device_status"] = yan_b200.read_device_status()
+        comm.close()
+    except Exception as e:  # peer mapping unavailable (e.g. ranks without peer access): the NCCL numbers stand alone
+        results["two-shot peer allreduce"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+    return {"workload": f"C5 row-parallel GEMM + allreduce M={m} N={n} K={k} (K/{world} per GPU, bf16 partials)",
             "allreduce_bytes": 2 * m * n, **results}
 
 

@@ -193,6 +193,17 @@ void yan_b200_allreduce_bf16_two_shot(void* const* data, void* const* signals, i
                                       unsigned int counter_target, int num_ctas, void* stream, int* return_code);
 
 /*
+ * The same allreduce with the sum formed inside the NVSwitch (multimem.ld_reduce / multimem.st, the instruction pair
+ * of comm/gemm_allreduce.cu:57-60,386-395).  `multicast` is the multicast address of the ranks' buffers: memory
+ * that every rank has bound to one multicast object (cuMulticastBindMem; torch.distributed._symmetric_memory provides
+ * such allocations).  signals[r] are ordinary peer addresses as above.  Everything else as
+ * yan_b200_allreduce_bf16_two_shot.
+ */
+void yan_b200_allreduce_bf16_in_switch(void* multicast, void* const* signals, int world, int rank,
+                                       unsigned long long elem_begin, unsigned long long elem_count, unsigned int epoch,
+                                       unsigned int counter_target, int num_ctas, void* stream, int* return_code);
+
+/*
  * Programmatic dependent launch for the weight-streaming (M <= 64) kernel.  When enabled, that kernel is
  * launched with cudaLaunchAttributeProgrammaticStreamSerialization: its weight loads (rhs) may start while the
  * previous kernel of the stream is still running; activations, scales of the activations and the output are

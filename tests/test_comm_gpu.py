@@ -87,9 +87,19 @@ def _two_shot_worker(rank, world, port, results):
         from oracle import ref
         from yan_b200.comm import TwoShotAllreduce, gemm_allreduce as ga
         m, n, k = 512, 1024, 2048
-        ok = True
-        for device_barriers in (True, False):
-            comm = TwoShotAllreduce(m, n, device_barriers=device_barriers)
+        checks = {}
+
+        def same(got, want, exact):
+            # The peer kernel adds in fp32 in rank order and rounds once (reproducible bit for bit); the switch's adder
+            # is only required to be within one bf16 step of that.
+            if exact:
+                return bool(torch.equal(got, want))
+            err = (got.float() - want.float()).abs()
+            return bool((err <= want.float().abs() * 2.0 ** -7 + 1e-30).all())
+
+        for device_barriers, in_switch in ((True, False), (False, False), (True, True)):
+            tag = f"barriers={device_barriers},in_switch={in_switch}"
+            comm = TwoShotAllreduce(m, n, device_barriers=device_barriers, in_switch=in_switch)
             # 1. the collective alone: every rank can reproduce every rank's input from its seed
             parts = []
             for r in range(world):
@@ -102,13 +112,14 @@ def _two_shot_worker(rank, world, port, results):
             comm.buffer.copy_(parts[rank])
             comm.reduce_rows()
             torch.cuda.synchronize()
-            ok &= torch.equal(comm.buffer, want)
+            checks[f"{tag}: whole tensor"] = same(comm.buffer, want, not in_switch)
             # 2. a row range only: the rows outside keep this rank's own values
             comm.buffer.copy_(parts[rank])
             comm.reduce_rows(128, 384, num_ctas=7)
             torch.cuda.synchronize()
-            ok &= torch.equal(comm.buffer[128:384], want[128:384])
-            ok &= torch.equal(comm.buffer[:128], parts[rank][:128]) and torch.equal(comm.buffer[384:], parts[rank][384:])
+            checks[f"{tag}: row range"] = same(comm.buffer[128:384], want[128:384], not in_switch)
+            checks[f"{tag}: rows outside untouched"] = bool(
+                torch.equal(comm.buffer[:128], parts[rank][:128]) and torch.equal(comm.buffer[384:], parts[rank][384:]))
             # 3. the K-split GEMM on top of it, whole and in two overlapped row chunks
             a, b = ref.make_inputs(m, n, k, seed=3)
             lhs, rhs = ref.per_token_cast_to_fp8(a), ref.per_block_cast_to_fp8(b)
@@ -121,12 +132,14 @@ def _two_shot_worker(rank, world, port, results):
             for chunks in (1, 2):
                 out = ga.gemm_k_split_two_shot(lhs_local, rhs_k, comm, num_chunks=chunks)
                 torch.cuda.synchronize()
-                ok &= ref.rel_frobenius(out.cpu(), d_split) <= 2e-3
-                if world == 2:  # the sum of two bf16 numbers rounded once: the same whoever adds them
-                    ok &= torch.equal(out, nccl)
-            ok &= yan_b200.read_device_status() == 0
+                # the switch's adder does not round to nearest (measured: ~3e-3 against the round-to-nearest sum)
+                tol = 6e-3 if in_switch else 2e-3
+                checks[f"{tag}: K-split {chunks} chunk(s) vs oracle"] = ref.rel_frobenius(out.cpu(), d_split) <= tol
+                if world == 2 and not in_switch:  # the sum of two bf16 numbers rounded once: the same whoever adds them
+                    checks[f"{tag}: K-split {chunks} chunk(s) vs NCCL"] = bool(torch.equal(out, nccl))
+            checks[f"{tag}: status"] = yan_b200.read_device_status() == 0
             comm.close()
-        results[rank] = bool(ok)
+        results[rank] = {name: bool(v) for name, v in checks.items()}
     finally:
         dist.destroy_process_group()
 
@@ -147,4 +160,6 @@ def test_two_shot_peer_allreduce_and_k_split(cuda_lib):
         p.join(240)
         assert not p.is_alive(), "rank did not finish"
     assert [p.exitcode for p in procs] == [0, 0]
-    assert dict(results) == {0: True, 1: True}
+    failed = {r: [name for name, v in dict(results[r]).items() if not v] for r in range(world)}
+    assert failed == {0: [], 1: []}, failed
+    assert len(dict(results[0])) >= 20

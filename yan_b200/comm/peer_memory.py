@@ -79,21 +79,55 @@ class PeerSharedTensor:
         self._keys = []
 
 
+class MulticastSharedTensor:
+    """Like PeerSharedTensor, with the ranks' tensors additionally bound to one NVSwitch multicast object:
+    `multicast_ptr` addresses all copies at once (multimem instructions).  The allocation and the handle exchange are
+    PyTorch's (torch.distributed._symmetric_memory); this class only reads the addresses."""
+
+    def __init__(self, shape, dtype: torch.dtype, group: Optional[dist.ProcessGroup] = None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.local = symm_mem.empty(shape, dtype=dtype, device="cuda")
+        self._handle = symm_mem.rendezvous(self.local, group if group is not None else dist.group.WORLD)
+        self.ptrs = [int(p) for p in self._handle.buffer_ptrs]
+        self.multicast_ptr = int(self._handle.multicast_ptr)
+        if self.multicast_ptr == 0:
+            raise RuntimeError("this allocation has no multicast mapping (no NVSwitch multicast support)")
+        self.local.zero_()
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+
+    def ptr_array(self):
+        return (ctypes.c_void_p * self.world)(*self.ptrs)
+
+    def close(self) -> None:
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        self._handle = None
+
+
 class TwoShotAllreduce:
     """In-place sum over the ranks of a peer-shared bf16 matrix [M, N] (`buffer`): the GEMM writes its partial product
     into `buffer`, `reduce_rows` leaves the sum of all ranks' partials there on every rank.
 
     device_barriers=True : the kernel orders the ranks itself with epoch flags in peer memory (bounded waits).
     device_barriers=False: the ranks are ordered by a one-element NCCL allreduce before and after the kernel.
+    in_switch=False: each rank loads its slice from every buffer, adds, and stores the sum to every buffer.
+    in_switch=True : the buffers are bound to an NVSwitch multicast object and the sum is formed in the switch
+                     (multimem.ld_reduce / multimem.st); less NVLink traffic per GPU, needs multicast support.
     """
 
     def __init__(self, m: int, n: int, group: Optional[dist.ProcessGroup] = None, device_barriers: bool = True,
-                 num_ctas: Optional[int] = None):
+                 num_ctas: Optional[int] = None, in_switch: bool = False):
         assert n % 8 == 0, "rows are moved in 16-byte vectors"
         self.group = group
         self.m, self.n = m, n
+        self.in_switch = in_switch
         # one allocation: the matrix, then the signal block
-        self._arena = PeerSharedTensor((m * n * 2 + SIGNAL_BYTES,), torch.uint8, group)
+        arena_type = MulticastSharedTensor if in_switch else PeerSharedTensor
+        self._arena = arena_type((m * n * 2 + SIGNAL_BYTES,), torch.uint8, group)
         self.rank, self.world = self._arena.rank, self._arena.world
         assert 2 <= self.world <= 8
         self.buffer = self._arena.local[: m * n * 2].view(torch.bfloat16).view(m, n)
@@ -101,7 +135,7 @@ class TwoShotAllreduce:
         self._signals = (ctypes.c_void_p * self.world)(*[p + m * n * 2 for p in self._arena.ptrs])
         self.device_barriers = device_barriers
         sms = torch.cuda.get_device_properties(self.buffer.device).multi_processor_count
-        self.num_ctas = num_ctas or 2 * sms
+        self.num_ctas = num_ctas or sms  # one CTA per SM saturates the links (measured)
         self._epoch = 0
         self._cta_count = 0
         self._token = torch.zeros(1, dtype=torch.float32, device="cuda")
@@ -114,15 +148,18 @@ class TwoShotAllreduce:
         ctas = num_ctas or self.num_ctas
         stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
         begin, count = row_begin * self.n, (row_end - row_begin) * self.n
+        if self.in_switch:
+            name, target = "yan_b200_allreduce_bf16_in_switch", ctypes.c_void_p(self._arena.multicast_ptr)
+        else:
+            name, target = "yan_b200_allreduce_bf16_two_shot", self._data
         if self.device_barriers:
             self._epoch += 1
             self._cta_count = (self._cta_count + ctas) & 0xFFFFFFFF
-            _lib.call("yan_b200_allreduce_bf16_two_shot", self._data, self._signals, self.world, self.rank, begin, count,
-                      self._epoch, self._cta_count, ctas, stream)
+            _lib.call(name, target, self._signals, self.world, self.rank, begin, count, self._epoch, self._cta_count,
+                      ctas, stream)
         else:
             dist.all_reduce(self._token, group=self.group)  # every rank's partial is complete
-            _lib.call("yan_b200_allreduce_bf16_two_shot", self._data, None, self.world, self.rank, begin, count, 0, 0,
-                      ctas, stream)
+            _lib.call(name, target, None, self.world, self.rank, begin, count, 0, 0, ctas, stream)
             dist.all_reduce(self._token, group=self.group)  # every rank's stores have landed
 
     def close(self) -> None:

@@ -436,6 +436,27 @@ YAN_EXPORT void yan_b200_allreduce_bf16_two_shot(void* const* data, void* const*
     set_rc(return_code, yan::launch_two_shot_allreduce_bf16(a, static_cast<cudaStream_t>(stream)));
 }
 
+YAN_EXPORT void yan_b200_allreduce_bf16_in_switch(void* multicast, void* const* signals, int world, int rank,
+                                                  unsigned long long elem_begin, unsigned long long elem_count,
+                                                  unsigned int epoch, unsigned int counter_target, int num_ctas,
+                                                  void* stream, int* return_code) {
+    if (multicast == nullptr || world < 2 || world > yan::kMaxPeers || (epoch != 0 && signals == nullptr))
+        return set_rc(return_code, yan::kBadArgument);
+    yan::AllreduceArgs a;
+    a.multicast = multicast;
+    for (int r = 0; r < world; ++r) a.signals.p[r] = (epoch != 0) ? signals[r] : nullptr;
+    a.world = world;
+    a.rank = rank;
+    a.elem_begin = elem_begin;
+    a.elem_count = elem_count;
+    a.epoch = epoch;
+    a.counter_target = counter_target;
+    a.num_ctas = num_ctas;
+    a.status = status_word_of_current_device();
+    a.timeout_ns = g_timeout_ns;
+    set_rc(return_code, yan::launch_two_shot_allreduce_bf16(a, static_cast<cudaStream_t>(stream)));
+}
+
 YAN_EXPORT void yan_b200_set_programmatic_dependent_launch(int enabled) { g_programmatic_launch = enabled; }
 
 YAN_EXPORT void yan_b200_set_wait_timeout_ns(unsigned long long timeout_ns) {

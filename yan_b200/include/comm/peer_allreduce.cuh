@@ -10,7 +10,8 @@
 //   all-gather    : it stores the result to the same slice of all W buffers.
 // Inbound (loads) and outbound (stores) traffic run at the same time, NVLink being full duplex; per GPU
 // (W-1)/W of the tensor crosses each direction once, the minimum for an allreduce without in-switch reduction.
-// Plain ld/st on peer pointers only (no multimem, no bulk copies).
+// Plain ld/st on peer pointers only.  A second kernel does the same collective with multimem instructions (the sum
+// is formed inside the switch) for buffers that are bound to a multicast object.
 //
 // Ordering between ranks, with epoch > 0, is part of the kernel: on entry a rank tells every peer that its partial
 // is complete (st.release.sys of the epoch into the peer's `arrive` slot) and waits until all peers said so; on exit,
@@ -90,6 +91,43 @@ __device__ __forceinline__ void accumulate(float (&acc)[8], const uint4& v) {
 
 }  // namespace comm_detail
 
+// Entry barrier: tells every peer that this rank's input is complete and waits for the same from all.
+// Returns false (after recording the status) when a wait ran out; the whole CTA gets the same answer.
+template <int W>
+__device__ __forceinline__ bool enter_collective(const PeerPtrs& signals, PeerSignals* my_signals, int rank,
+                                                 uint32_t epoch, int* status, unsigned long long timeout_ns) {
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (blockIdx.x == 0 && threadIdx.x < W)
+        comm_detail::st_release_sys(&static_cast<PeerSignals*>(signals.p[threadIdx.x])->arrive[rank], epoch);
+    if (threadIdx.x < W && !comm_detail::wait_flag(&my_signals->arrive[threadIdx.x], epoch, timeout_ns)) {
+        s_ok = 0;
+        if (status != nullptr) atomicCAS(status, 0, (static_cast<int>(kDeviceTimeout) << 8) | 16);
+    }
+    __syncthreads();
+    return s_ok != 0;
+}
+
+// Exit barrier: after a system-scope fence by every thread, the last CTA of the grid tells every peer that this rank's
+// stores are done and waits for the same from all.
+template <int W>
+__device__ __forceinline__ void leave_collective(const PeerPtrs& signals, PeerSignals* my_signals, int rank,
+                                                 uint32_t epoch, uint32_t counter_target, int* status,
+                                                 unsigned long long timeout_ns) {
+    __shared__ int s_last;
+    comm_detail::fence_sys();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(&my_signals->cta_counter, 1u) + 1u == counter_target);
+    __syncthreads();
+    if (s_last && threadIdx.x < W) {
+        comm_detail::fence_sys();
+        comm_detail::st_release_sys(&static_cast<PeerSignals*>(signals.p[threadIdx.x])->done[rank], epoch);
+        if (!comm_detail::wait_flag(&my_signals->done[threadIdx.x], epoch, timeout_ns) && status != nullptr)
+            atomicCAS(status, 0, (static_cast<int>(kDeviceTimeout) << 8) | 17);
+    }
+}
+
 // vec_begin / vec_count: the range to reduce, in 16-byte vectors (8 bf16) from the start of every buffer.
 template <int W>
 __global__ void __launch_bounds__(512)
@@ -97,68 +135,99 @@ __global__ void __launch_bounds__(512)
                                    const size_t vec_count, const uint32_t epoch, const uint32_t counter_target,
                                    int* status, const unsigned long long timeout_ns) {
     static_assert(W >= 2 && W <= kMaxPeers, "one NVSwitch box");
-    __shared__ int s_ok;
     PeerSignals* my_signals = static_cast<PeerSignals*>(signals.p[rank]);
-
-    // ---- entry: every rank's partial must be complete before anything is loaded ----
-    if (epoch != 0) {
-        if (threadIdx.x == 0) s_ok = 1;
-        __syncthreads();
-        if (blockIdx.x == 0 && threadIdx.x < W)
-            comm_detail::st_release_sys(&static_cast<PeerSignals*>(signals.p[threadIdx.x])->arrive[rank], epoch);
-        if (threadIdx.x < W && !comm_detail::wait_flag(&my_signals->arrive[threadIdx.x], epoch, timeout_ns)) {
-            s_ok = 0;
-            if (status != nullptr) atomicCAS(status, 0, (static_cast<int>(kDeviceTimeout) << 8) | 16);
-        }
-        __syncthreads();
-        if (s_ok == 0) return;  // inputs incomplete: leave the buffers alone (the host reads the status word)
-    }
+    // inputs incomplete after the bound: leave the buffers alone (the host reads the status word)
+    if (epoch != 0 && !enter_collective<W>(signals, my_signals, rank, epoch, status, timeout_ns)) return;
 
     // ---- this rank's slice: loads from all W buffers, one fp32 sum in rank order, stores to all W buffers ----
     const size_t per_rank = (vec_count + W - 1) / W;
     const size_t first = vec_begin + static_cast<size_t>(rank) * per_rank;
     const size_t last = (first + per_rank < vec_begin + vec_count) ? first + per_rank : vec_begin + vec_count;
+    // kUnroll vectors per thread and trip, all kUnroll * W loads issued before the first use.
+    constexpr int kUnroll = (W <= 2) ? 8 : (W <= 4) ? 4 : 2;
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-    for (size_t i = first + static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < last; i += stride) {
-        uint4 v[W];
+    for (size_t i0 = first + static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < last;
+         i0 += stride * kUnroll) {
+        uint4 v[kUnroll][W];
 #pragma unroll
-        for (int r = 0; r < W; ++r) v[r] = comm_detail::ld_sys_v4(static_cast<const uint4*>(data.p[r]) + i);
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int u = 0; u < kUnroll; ++u) {
+            const size_t i = i0 + u * stride;
+            if (i < last) {
 #pragma unroll
-        for (int r = 0; r < W; ++r) comm_detail::accumulate(acc, v[r]);
-        uint4 o;
-        __nv_bfloat162 t;
-        t = __floats2bfloat162_rn(acc[0], acc[1]); o.x = *reinterpret_cast<uint32_t*>(&t);
-        t = __floats2bfloat162_rn(acc[2], acc[3]); o.y = *reinterpret_cast<uint32_t*>(&t);
-        t = __floats2bfloat162_rn(acc[4], acc[5]); o.z = *reinterpret_cast<uint32_t*>(&t);
-        t = __floats2bfloat162_rn(acc[6], acc[7]); o.w = *reinterpret_cast<uint32_t*>(&t);
-#pragma unroll
-        for (int r = 0; r < W; ++r) {
-            const int peer = (rank + r) % W;  // spread the ranks over the destinations at any instant
-            static_cast<uint4*>(data.p[peer])[i] = o;
+                for (int r = 0; r < W; ++r) v[u][r] = comm_detail::ld_sys_v4(static_cast<const uint4*>(data.p[r]) + i);
+            }
         }
-    }
-
-    // ---- exit: all ranks' stores must have landed before this kernel may complete ----
-    if (epoch != 0) {
-        comm_detail::fence_sys();
-        __syncthreads();
-        __shared__ int s_last;
-        if (threadIdx.x == 0) s_last = (atomicAdd(&my_signals->cta_counter, 1u) + 1u == counter_target);
-        __syncthreads();
-        if (s_last) {
-            if (threadIdx.x < W) {
-                comm_detail::fence_sys();
-                comm_detail::st_release_sys(&static_cast<PeerSignals*>(signals.p[threadIdx.x])->done[rank], epoch);
-                if (!comm_detail::wait_flag(&my_signals->done[threadIdx.x], epoch, timeout_ns) && status != nullptr)
-                    atomicCAS(status, 0, (static_cast<int>(kDeviceTimeout) << 8) | 17);
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const size_t i = i0 + u * stride;
+            if (i < last) {
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int r = 0; r < W; ++r) comm_detail::accumulate(acc, v[u][r]);
+                uint4 o;
+                __nv_bfloat162 t;
+                t = __floats2bfloat162_rn(acc[0], acc[1]); o.x = *reinterpret_cast<uint32_t*>(&t);
+                t = __floats2bfloat162_rn(acc[2], acc[3]); o.y = *reinterpret_cast<uint32_t*>(&t);
+                t = __floats2bfloat162_rn(acc[4], acc[5]); o.z = *reinterpret_cast<uint32_t*>(&t);
+                t = __floats2bfloat162_rn(acc[6], acc[7]); o.w = *reinterpret_cast<uint32_t*>(&t);
+#pragma unroll
+                for (int r = 0; r < W; ++r) {
+                    const int peer = (rank + r) % W;  // spread the ranks over the destinations at any instant
+                    static_cast<uint4*>(data.p[peer])[i] = o;
+                }
             }
         }
     }
+
+    if (epoch != 0) leave_collective<W>(signals, my_signals, rank, epoch, counter_target, status, timeout_ns);
+}
+
+// The same collective with the sum formed inside the NVSwitch: `mc` is the multicast address of the buffers (memory
+// bound to one multicast object on all ranks).  multimem.ld_reduce returns the sum over all ranks' copies of a vector
+// (fp32 accumulation in the switch), multimem.st writes the result to all copies.  Per GPU about (1 + 1/W) of the
+// tensor crosses each NVLink direction instead of 2 (W-1)/W: at W = 8, 1.125 against 1.75.  This is the instruction
+// pair the reference's epilogue uses (comm/gemm_allreduce.cu:57-60,386-395).
+template <int W>
+__global__ void __launch_bounds__(512)
+    in_switch_allreduce_bf16_kernel(uint4* mc, const PeerPtrs signals, const int rank, const size_t vec_begin,
+                                    const size_t vec_count, const uint32_t epoch, const uint32_t counter_target,
+                                    int* status, const unsigned long long timeout_ns) {
+    PeerSignals* my_signals = static_cast<PeerSignals*>(signals.p[rank]);
+    if (epoch != 0 && !enter_collective<W>(signals, my_signals, rank, epoch, status, timeout_ns)) return;
+
+    const size_t per_rank = (vec_count + W - 1) / W;
+    const size_t first = vec_begin + static_cast<size_t>(rank) * per_rank;
+    const size_t last = (first + per_rank < vec_begin + vec_count) ? first + per_rank : vec_begin + vec_count;
+    constexpr int kUnroll = 4;
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i0 = first + static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < last;
+         i0 += stride * kUnroll) {
+        uint4 v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const size_t i = i0 + u * stride;
+            if (i < last)
+                asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                             : "l"(mc + i)
+                             : "memory");
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const size_t i = i0 + u * stride;
+            if (i < last)
+                asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc + i),
+                             "r"(v[u].x), "r"(v[u].y), "r"(v[u].z), "r"(v[u].w)
+                             : "memory");
+        }
+    }
+
+    if (epoch != 0) leave_collective<W>(signals, my_signals, rank, epoch, counter_target, status, timeout_ns);
 }
 
 struct AllreduceArgs {
     PeerPtrs data{};     // the same-shaped bf16 buffer on every rank; entry [rank] is local, the others peer-mapped
+    void* multicast = nullptr;  // in-switch form only: the multicast address of the buffers (data is then unused)
     PeerPtrs signals{};  // PeerSignals blocks, same convention; unused when epoch == 0
     int world = 0, rank = 0;
     size_t elem_begin = 0, elem_count = 0;  // range in bf16 elements, both multiples of 8
@@ -172,16 +241,23 @@ struct AllreduceArgs {
 inline int launch_two_shot_allreduce_bf16(const AllreduceArgs& a, cudaStream_t stream) {
     if (a.world < 2 || a.world > kMaxPeers || a.rank < 0 || a.rank >= a.world || a.num_ctas <= 0) return kBadArgument;
     if (a.elem_begin % 8 != 0 || a.elem_count % 8 != 0 || a.elem_count == 0) return kBadArgument;
+    if (a.multicast != nullptr && reinterpret_cast<uintptr_t>(a.multicast) % 16 != 0) return kBadArgument;
     for (int r = 0; r < a.world; ++r) {
-        if (a.data.p[r] == nullptr || reinterpret_cast<uintptr_t>(a.data.p[r]) % 16 != 0) return kBadArgument;
+        if (a.multicast == nullptr && (a.data.p[r] == nullptr || reinterpret_cast<uintptr_t>(a.data.p[r]) % 16 != 0))
+            return kBadArgument;
         if (a.epoch != 0 && (a.signals.p[r] == nullptr || reinterpret_cast<uintptr_t>(a.signals.p[r]) % 4 != 0))
             return kBadArgument;
     }
     const size_t vb = a.elem_begin / 8, vc = a.elem_count / 8;
     const dim3 grid(static_cast<unsigned>(a.num_ctas)), block(512);
 #define YAN_LAUNCH_TWO_SHOT(W)                                                                                   \
-    two_shot_allreduce_bf16_kernel<W><<<grid, block, 0, stream>>>(a.data, a.signals, a.rank, vb, vc, a.epoch,    \
-                                                                  a.counter_target, a.status, a.timeout_ns)
+    if (a.multicast != nullptr)                                                                                  \
+        in_switch_allreduce_bf16_kernel<W><<<grid, block, 0, stream>>>(static_cast<uint4*>(a.multicast), a.signals, \
+                                                                       a.rank, vb, vc, a.epoch, a.counter_target, \
+                                                                       a.status, a.timeout_ns);                  \
+    else                                                                                                         \
+        two_shot_allreduce_bf16_kernel<W><<<grid, block, 0, stream>>>(a.data, a.signals, a.rank, vb, vc, a.epoch, \
+                                                                      a.counter_target, a.status, a.timeout_ns)
     switch (a.world) {
         case 2: YAN_LAUNCH_TWO_SHOT(2); break;
         case 3: YAN_LAUNCH_TWO_SHOT(3); break;
