@@ -331,18 +331,21 @@ def bench_k_split(rank: int, world: int, dist, steps: int = 10) -> dict:
     try:
         from yan_b200.comm import TwoShotAllreduce
         comm = TwoShotAllreduce(m, n)
-        for label, chunks in (("two-shot peer allreduce", 1), ("two-shot peer allreduce, 4 row chunks overlapped", 4)):
+        variants = (("", 1, 24), (", 2 row chunks overlapped (24 SMs to the collective)", 2, 24),
+                    (", 2 row chunks overlapped (64 SMs to the collective)", 2, 64),
+                    (", 4 row chunks overlapped (64 SMs to the collective)", 4, 64))
+        for suffix, chunks, comm_sms in variants:
             def step():
                 yan_b200.per_token_cast_to_fp8(a, out=lhs)
-                ga.gemm_k_split_two_shot(lhs, rhs, comm, num_chunks=chunks, comm_stream=comm_stream)
-            results[label] = _time_k_split(step, dist, steps, m, n, k)
+                ga.gemm_k_split_two_shot(lhs, rhs, comm, num_chunks=chunks, comm_sms=comm_sms, comm_stream=comm_stream)
+            results["two-shot peer allreduce" + suffix] = _time_k_split(step, dist, steps, m, n, k)
         try:
             comm_sw = TwoShotAllreduce(m, n, in_switch=True)
-            for label, chunks in (("in-switch peer allreduce", 1), ("in-switch peer allreduce, 4 row chunks overlapped", 4)):
+            for suffix, chunks, comm_sms in variants:
                 def step():
                     yan_b200.per_token_cast_to_fp8(a, out=lhs)
-                    ga.gemm_k_split_two_shot(lhs, rhs, comm_sw, num_chunks=chunks, comm_stream=comm_stream)
-                results[label] = _time_k_split(step, dist, steps, m, n, k)
+                    ga.gemm_k_split_two_shot(lhs, rhs, comm_sw, num_chunks=chunks, comm_sms=comm_sms, comm_stream=comm_stream)
+                results["in-switch peer allreduce" + suffix] = _time_k_split(step, dist, steps, m, n, k)
             results["allreduce alone, in-switch"] = _time_k_split(lambda: comm_sw.reduce_rows(), dist, steps, m, n, k, flops=False)
             comm_sw.close()
         except Exception as e:

@@ -186,11 +186,15 @@ void yan_b200_ipc_close(void* base, int* return_code);
  *   included), identically on every rank.  Waits are bounded (yan_b200_set_wait_timeout_ns) and report
  *   (YAN_B200_DEVICE_TIMEOUT << 8) | 16 or 17 through the status word.
  * epoch == 0: no device-side waiting; the caller orders the ranks before and after the call.
- * elem_begin and elem_count are multiples of 8; 2 <= world <= 8; num_ctas > 0 (CTAs of 512 threads).
+ * elem_begin and elem_count are multiples of 8; 2 <= world <= 8; num_ctas > 0.
+ * exclusive_sms == 0: CTAs of 512 threads, the faster shape when the collective has the GPU to itself.
+ * exclusive_sms != 0: CTAs of 1024 threads that fill an SM each, so the collective occupies exactly num_ctas SMs and a
+ *   GEMM running beside it on another stream (given the other SMs through its num_sms) is not displaced.
  */
 void yan_b200_allreduce_bf16_two_shot(void* const* data, void* const* signals, int world, int rank,
                                       unsigned long long elem_begin, unsigned long long elem_count, unsigned int epoch,
-                                      unsigned int counter_target, int num_ctas, void* stream, int* return_code);
+                                      unsigned int counter_target, int num_ctas, int exclusive_sms, void* stream,
+                                      int* return_code);
 
 /*
  * The same allreduce with the sum formed inside the NVSwitch (multimem.ld_reduce / multimem.st, the instruction pair
@@ -201,7 +205,8 @@ void yan_b200_allreduce_bf16_two_shot(void* const* data, void* const* signals, i
  */
 void yan_b200_allreduce_bf16_in_switch(void* multicast, void* const* signals, int world, int rank,
                                        unsigned long long elem_begin, unsigned long long elem_count, unsigned int epoch,
-                                       unsigned int counter_target, int num_ctas, void* stream, int* return_code);
+                                       unsigned int counter_target, int num_ctas, int exclusive_sms, void* stream,
+                                       int* return_code);
 
 /*
  * Programmatic dependent launch for the weight-streaming (M <= 64) kernel.  When enabled, that kernel is

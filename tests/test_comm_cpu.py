@@ -73,7 +73,7 @@ def _worker(rank: int, world: int, port: int, mode: str, results):
                     self.buffer = torch.zeros(m, n, dtype=torch.bfloat16)
                     self.calls = []
 
-                def reduce_rows(self, r0=0, r1=None, num_ctas=None):
+                def reduce_rows(self, r0=0, r1=None, num_ctas=None, exclusive_sms=False):
                     self.calls.append((r0, r1))
                     parts = [torch.empty(r1 - r0, n) for _ in range(world)]
                     dist.all_gather(parts, self.buffer[r0:r1].float())

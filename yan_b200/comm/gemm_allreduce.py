@@ -122,7 +122,7 @@ def gemm_k_split_allreduce(lhs_shard: Operand, rhs_shard: Operand, out: torch.Te
     return out
 
 
-def gemm_k_split_two_shot(lhs_shard: Operand, rhs_shard: Operand, comm, num_chunks: int = 1, comm_sms: int = 16,
+def gemm_k_split_two_shot(lhs_shard: Operand, rhs_shard: Operand, comm, num_chunks: int = 1, comm_sms: int = 24,
                           gemm_fn: Optional[Callable] = None,
                           comm_stream: Optional["torch.cuda.Stream"] = None) -> torch.Tensor:
     """K-split GEMM whose partials are summed by the two-shot peer-memory kernel instead of NCCL.
@@ -148,7 +148,6 @@ def gemm_k_split_two_shot(lhs_shard: Operand, rhs_shard: Operand, comm, num_chun
     comm_stream = comm_stream or torch.cuda.Stream(device=buf.device)
     main = torch.cuda.current_stream(buf.device)
     all_sms = get_num_sms()
-    sm_threads = 2048 // 512  # CTAs of the allreduce kernel one SM can hold
     try:
         for i, (r0, r1) in enumerate(bounds):
             # the first chunk has the GPU to itself; later ones share it with the allreduce of the chunk before
@@ -159,7 +158,7 @@ def gemm_k_split_two_shot(lhs_shard: Operand, rhs_shard: Operand, comm, num_chun
             with torch.cuda.stream(comm_stream):
                 comm_stream.wait_event(ready)
                 last = i + 1 == len(bounds)
-                comm.reduce_rows(r0, r1, num_ctas=None if last else comm_sms * sm_threads)
+                comm.reduce_rows(r0, r1, num_ctas=None if last else comm_sms, exclusive_sms=not last)
     finally:
         set_num_sms(all_sms)
     done = torch.cuda.Event()

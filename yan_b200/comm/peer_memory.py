@@ -140,9 +140,11 @@ class TwoShotAllreduce:
         self._cta_count = 0
         self._token = torch.zeros(1, dtype=torch.float32, device="cuda")
 
-    def reduce_rows(self, row_begin: int = 0, row_end: Optional[int] = None, num_ctas: Optional[int] = None) -> None:
+    def reduce_rows(self, row_begin: int = 0, row_end: Optional[int] = None, num_ctas: Optional[int] = None,
+                    exclusive_sms: bool = False) -> None:
         """Allreduce of rows [row_begin, row_end) on the current stream.  Every rank makes the same calls in the same
-        order."""
+        order.  exclusive_sms: the kernel's CTAs fill one SM each, so it occupies exactly `num_ctas` SMs (for running
+        beside a GEMM that was given the other SMs)."""
         row_end = self.m if row_end is None else row_end
         assert 0 <= row_begin < row_end <= self.m
         ctas = num_ctas or self.num_ctas
@@ -156,10 +158,10 @@ class TwoShotAllreduce:
             self._epoch += 1
             self._cta_count = (self._cta_count + ctas) & 0xFFFFFFFF
             _lib.call(name, target, self._signals, self.world, self.rank, begin, count, self._epoch, self._cta_count,
-                      ctas, stream)
+                      ctas, int(exclusive_sms), stream)
         else:
             dist.all_reduce(self._token, group=self.group)  # every rank's partial is complete
-            _lib.call(name, target, None, self.world, self.rank, begin, count, 0, 0, ctas, stream)
+            _lib.call(name, target, None, self.world, self.rank, begin, count, 0, 0, ctas, int(exclusive_sms), stream)
             dist.all_reduce(self._token, group=self.group)  # every rank's stores have landed
 
     def close(self) -> None:

@@ -416,7 +416,7 @@ YAN_EXPORT void yan_b200_ipc_close(void* base, int* return_code) {
 YAN_EXPORT void yan_b200_allreduce_bf16_two_shot(void* const* data, void* const* signals, int world, int rank,
                                                  unsigned long long elem_begin, unsigned long long elem_count,
                                                  unsigned int epoch, unsigned int counter_target, int num_ctas,
-                                                 void* stream, int* return_code) {
+                                                 int exclusive_sms, void* stream, int* return_code) {
     if (data == nullptr || world < 2 || world > yan::kMaxPeers || (epoch != 0 && signals == nullptr))
         return set_rc(return_code, yan::kBadArgument);
     yan::AllreduceArgs a;
@@ -431,6 +431,7 @@ YAN_EXPORT void yan_b200_allreduce_bf16_two_shot(void* const* data, void* const*
     a.epoch = epoch;
     a.counter_target = counter_target;
     a.num_ctas = num_ctas;
+    a.exclusive = exclusive_sms != 0;
     a.status = status_word_of_current_device();
     a.timeout_ns = g_timeout_ns;
     set_rc(return_code, yan::launch_two_shot_allreduce_bf16(a, static_cast<cudaStream_t>(stream)));
@@ -439,7 +440,7 @@ YAN_EXPORT void yan_b200_allreduce_bf16_two_shot(void* const* data, void* const*
 YAN_EXPORT void yan_b200_allreduce_bf16_in_switch(void* multicast, void* const* signals, int world, int rank,
                                                   unsigned long long elem_begin, unsigned long long elem_count,
                                                   unsigned int epoch, unsigned int counter_target, int num_ctas,
-                                                  void* stream, int* return_code) {
+                                                  int exclusive_sms, void* stream, int* return_code) {
     if (multicast == nullptr || world < 2 || world > yan::kMaxPeers || (epoch != 0 && signals == nullptr))
         return set_rc(return_code, yan::kBadArgument);
     yan::AllreduceArgs a;
@@ -452,6 +453,7 @@ YAN_EXPORT void yan_b200_allreduce_bf16_in_switch(void* multicast, void* const* 
     a.epoch = epoch;
     a.counter_target = counter_target;
     a.num_ctas = num_ctas;
+    a.exclusive = exclusive_sms != 0;
     a.status = status_word_of_current_device();
     a.timeout_ns = g_timeout_ns;
     set_rc(return_code, yan::launch_two_shot_allreduce_bf16(a, static_cast<cudaStream_t>(stream)));

@@ -30,6 +30,14 @@
 namespace yan {
 
 constexpr int kMaxPeers = 8;
+// Two CTA shapes.  512 threads with about sixteen 16-byte loads in flight per thread is the faster one when the
+// collective has the GPU to itself (8 GPUs, 64 MiB: 196 us against 219 us).  1024 threads at <= 64 registers fill an SM,
+// so a grid of n such CTAs occupies exactly n SMs however the hardware places it and a GEMM running beside the
+// collective keeps the others (smaller CTAs are spread one per SM over the whole GPU and the persistent GEMM loses
+// those SMs).  Bandwidth grows with the number of SMs issuing peer accesses -- an SM sustains roughly 20 GB/s of
+// peer traffic -- so the collective is only link-bound from about 64 SMs up.
+constexpr int kAllreduceThreads = 512;
+constexpr int kAllreduceThreadsExclusive = 1024;
 
 struct PeerPtrs {
     void* p[kMaxPeers];
@@ -129,8 +137,8 @@ __device__ __forceinline__ void leave_collective(const PeerPtrs& signals, PeerSi
 }
 
 // vec_begin / vec_count: the range to reduce, in 16-byte vectors (8 bf16) from the start of every buffer.
-template <int W>
-__global__ void __launch_bounds__(512)
+template <int W, int kThreads>
+__global__ void __launch_bounds__(kThreads)
     two_shot_allreduce_bf16_kernel(const PeerPtrs data, const PeerPtrs signals, const int rank, const size_t vec_begin,
                                    const size_t vec_count, const uint32_t epoch, const uint32_t counter_target,
                                    int* status, const unsigned long long timeout_ns) {
@@ -143,8 +151,10 @@ __global__ void __launch_bounds__(512)
     const size_t per_rank = (vec_count + W - 1) / W;
     const size_t first = vec_begin + static_cast<size_t>(rank) * per_rank;
     const size_t last = (first + per_rank < vec_begin + vec_count) ? first + per_rank : vec_begin + vec_count;
-    // kUnroll vectors per thread and trip, all kUnroll * W loads issued before the first use.
-    constexpr int kUnroll = (W <= 2) ? 8 : (W <= 4) ? 4 : 2;
+    // kUnroll vectors per thread and trip, all kUnroll * W loads issued before the first use (what the register
+    // budget of the CTA shape allows: about 16 vectors at 512 threads, 8 at 1024).
+    constexpr int kVectors = (kThreads <= 512) ? 16 : 8;
+    constexpr int kUnroll = (kVectors / W) > 0 ? (kVectors / W) : 1;
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
     for (size_t i0 = first + static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < last;
          i0 += stride * kUnroll) {
@@ -187,8 +197,8 @@ __global__ void __launch_bounds__(512)
 // (fp32 accumulation in the switch), multimem.st writes the result to all copies.  Per GPU about (1 + 1/W) of the
 // tensor crosses each NVLink direction instead of 2 (W-1)/W: at W = 8, 1.125 against 1.75.  This is the instruction
 // pair the reference's epilogue uses (comm/gemm_allreduce.cu:57-60,386-395).
-template <int W>
-__global__ void __launch_bounds__(512)
+template <int W, int kThreads>
+__global__ void __launch_bounds__(kThreads)
     in_switch_allreduce_bf16_kernel(uint4* mc, const PeerPtrs signals, const int rank, const size_t vec_begin,
                                     const size_t vec_count, const uint32_t epoch, const uint32_t counter_target,
                                     int* status, const unsigned long long timeout_ns) {
@@ -234,6 +244,7 @@ struct AllreduceArgs {
     uint32_t epoch = 0;                     // 0: the caller orders the ranks; otherwise a per-launch growing number
     uint32_t counter_target = 0;            // sum of the grid sizes of all launches so far on this rank, this one included
     int num_ctas = 0;                       // grid size (> 0)
+    bool exclusive = false;                 // true: 1024-thread CTAs, one per SM: the grid occupies exactly num_ctas SMs
     int* status = nullptr;
     unsigned long long timeout_ns = 2000000000ull;
 };
@@ -249,25 +260,32 @@ inline int launch_two_shot_allreduce_bf16(const AllreduceArgs& a, cudaStream_t s
             return kBadArgument;
     }
     const size_t vb = a.elem_begin / 8, vc = a.elem_count / 8;
-    const dim3 grid(static_cast<unsigned>(a.num_ctas)), block(512);
-#define YAN_LAUNCH_TWO_SHOT(W)                                                                                   \
-    if (a.multicast != nullptr)                                                                                  \
-        in_switch_allreduce_bf16_kernel<W><<<grid, block, 0, stream>>>(static_cast<uint4*>(a.multicast), a.signals, \
-                                                                       a.rank, vb, vc, a.epoch, a.counter_target, \
-                                                                       a.status, a.timeout_ns);                  \
-    else                                                                                                         \
-        two_shot_allreduce_bf16_kernel<W><<<grid, block, 0, stream>>>(a.data, a.signals, a.rank, vb, vc, a.epoch, \
-                                                                      a.counter_target, a.status, a.timeout_ns)
-    switch (a.world) {
-        case 2: YAN_LAUNCH_TWO_SHOT(2); break;
-        case 3: YAN_LAUNCH_TWO_SHOT(3); break;
-        case 4: YAN_LAUNCH_TWO_SHOT(4); break;
-        case 5: YAN_LAUNCH_TWO_SHOT(5); break;
-        case 6: YAN_LAUNCH_TWO_SHOT(6); break;
-        case 7: YAN_LAUNCH_TWO_SHOT(7); break;
-        default: YAN_LAUNCH_TWO_SHOT(8); break;
+    const dim3 grid(static_cast<unsigned>(a.num_ctas));
+#define YAN_LAUNCH_ALLREDUCE(W, T)                                                                                  \
+    if (a.multicast != nullptr)                                                                                     \
+        in_switch_allreduce_bf16_kernel<W, T><<<grid, T, 0, stream>>>(static_cast<uint4*>(a.multicast), a.signals,  \
+                                                                      a.rank, vb, vc, a.epoch, a.counter_target,    \
+                                                                      a.status, a.timeout_ns);                      \
+    else                                                                                                            \
+        two_shot_allreduce_bf16_kernel<W, T><<<grid, T, 0, stream>>>(a.data, a.signals, a.rank, vb, vc, a.epoch,    \
+                                                                     a.counter_target, a.status, a.timeout_ns)
+#define YAN_LAUNCH_ALLREDUCE_W(W)                                          \
+    if (a.exclusive) {                                                     \
+        YAN_LAUNCH_ALLREDUCE(W, kAllreduceThreadsExclusive);               \
+    } else {                                                               \
+        YAN_LAUNCH_ALLREDUCE(W, kAllreduceThreads);                        \
     }
-#undef YAN_LAUNCH_TWO_SHOT
+    switch (a.world) {
+        case 2: YAN_LAUNCH_ALLREDUCE_W(2) break;
+        case 3: YAN_LAUNCH_ALLREDUCE_W(3) break;
+        case 4: YAN_LAUNCH_ALLREDUCE_W(4) break;
+        case 5: YAN_LAUNCH_ALLREDUCE_W(5) break;
+        case 6: YAN_LAUNCH_ALLREDUCE_W(6) break;
+        case 7: YAN_LAUNCH_ALLREDUCE_W(7) break;
+        default: YAN_LAUNCH_ALLREDUCE_W(8) break;
+    }
+#undef YAN_LAUNCH_ALLREDUCE_W
+#undef YAN_LAUNCH_ALLREDUCE
     return cudaGetLastError() == cudaSuccess ? kOk : kCommFailed;
 }
 
