@@ -52,7 +52,7 @@ const char* yan_b200_return_code_string(int code);
  * FP8 GEMM, D = A . B^T with per-128-K scale promotion.  Replaces the launch the reference's template
  * describes: yan/jit_kernels/gemm.py:9-31 (`Gemm<...>::run(out, rhs_scales, nullptr, m, descs..., stream,
  * num_sms, smem_size)`) and the kernel yan/include/gemm/fp8_gemm.cuh:32-197.
- * block_n: 0 = choose, 32, 64, 128 or 256 = tile width of the general kernel, 1 = the weight-streaming kernel
+ * block_n: 0 = choose; 32, 64, 96, 128, 160, 192, 224 or 256 = tile width of the general kernel; 1 = the weight-streaming kernel
  * for M <= 64 (split-K over a pair of CTAs), 2 = the weight-streaming kernel for M <= 32 that keeps all of K in one
  * CTA (YAN_B200_BAD_ARGUMENT when the problem does not fit the kernel asked for).
  * num_sms: CTAs of the persistent grid (<= device SMs).

@@ -41,7 +41,7 @@ def _run(lhs, rhs, block_n=0, out=None):
     return out
 
 
-@pytest.mark.parametrize("block_n", [0, 32, 64, 128, 256])
+@pytest.mark.parametrize("block_n", [0, 32, 64, 96, 128, 160, 192, 224, 256])
 def test_config1_all_tiles(cuda_lib, block_n):
     """M=256 N=1024 K=1024 seed 0: the CPU-runnable configuration."""
     lhs, rhs = _operands(256, 1024, 1024)
@@ -129,6 +129,21 @@ def test_stacked_k_kernel_limits(cuda_lib):
     assert _lib.call_rc(f, p, p, p, p, p, 16, 128, 768, 128, stream, sms, 2) == 1    # K not a multiple of 512
     assert _lib.call_rc(f, p, p, p, p, p, 16, 128, 8192, 128, stream, sms, 2) == 1   # more than 8 steps
     assert _lib.call_rc(f, p, p, p, p, p, 32, 128, 4096, 128, stream, sms, 2) == 1   # 8 steps x 128 TMEM columns
+
+
+@pytest.mark.parametrize("block_n", [96, 160, 192, 224])
+@pytest.mark.parametrize("m,n,k", [(300, 896, 512), (128, 1024, 1536), (257, 384, 256), (1024, 2560, 2048)])
+def test_tile_widths_that_straddle_scale_blocks(cuda_lib, block_n, m, n, k):
+    """BLOCK_N in {96, 160, 192, 224}: a promotion warpgroup's column range crosses a 128-column scale block at a
+    multiple of 16 (two B scales per k-block), N is not a multiple of the tile width (the last tile reads rows beyond
+    N as zeros and stores only the valid columns), and BLOCK_N/2 may end in a 16-column chunk."""
+    lhs, rhs = _operands(m, n, k, seed=block_n + m, outliers=True)
+    # make neighbouring scale blocks differ strongly so that a wrong block choice cannot pass the tolerance
+    q, s = rhs
+    s = s * (1.0 + torch.arange(s.shape[0], dtype=torch.float32).view(-1, 1) % 3)
+    rhs = (q, s)
+    d = _run(lhs, rhs, block_n)
+    _check(d.cpu(), ref.ref_gemm(lhs, rhs), f"m={m} n={n} k={k} block_n={block_n}")
 
 
 def test_long_k_many_tiles(cuda_lib):

@@ -23,7 +23,7 @@ LIB_DIR = os.path.join(PKG_DIR, "lib")
 OBJ_DIR = os.path.join(PKG_DIR, "lib", "obj")
 LIB_PATH = os.path.join(LIB_DIR, "libyan_b200.so")
 
-BLOCK_NS = (32, 64, 128, 256)
+BLOCK_NS = (32, 64, 96, 128, 160, 192, 224, 256)
 
 # No --use_fast_math: the quantizer's divisions and multiplies must be IEEE round-to-nearest.
 NVCC_FLAGS = [

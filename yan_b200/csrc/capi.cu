@@ -82,21 +82,24 @@ inline void set_rc(int* rc, int v) {
     if (rc != nullptr) *rc = v;
 }
 
-// Picks BLOCK_N by a wave model: cost = waves * (BLOCK_N + 64); the constant stands for the A tile and
-// the fixed per-tile work.  Large problems get 256 (fewest shared-memory bytes per flop), skinny ones
-// a narrower tile so that more SMs stream B.
+// Picks BLOCK_N by a wave model: cost = waves * (time of one tile relative to a 256-wide one).  The relative tile
+// times are measured (M = 8192, N = 28672, K = 8192, time * SMs / tiles): the promotion of a k-block has a large fixed
+// part, so a narrower tile is far from proportionally cheaper, and the widths whose half does not divide 128 pay for a
+// second B scale and a 16-column tail chunk.  Large problems therefore get 256; narrower tiles win when they fill the
+// machine better (few tiles, or a last wave of 256-wide tiles that is nearly empty).
 int choose_block_n(int m, int n, int num_sms) {
-    const int candidates[4] = {256, 128, 64, 32};
+    static const struct { int bn; double tile_cost; } candidates[8] = {
+        {256, 1.000}, {224, 0.985}, {192, 0.869}, {160, 0.823}, {128, 0.672}, {96, 0.62}, {64, 0.50}, {32, 0.42}};
     int best = 256;
-    long best_cost = -1;
-    for (int bn : candidates) {
-        if (bn > 32 && n < bn) continue;
-        const long tiles = static_cast<long>((m + 127) / 128) * ((n + bn - 1) / bn);
+    double best_cost = -1.0;
+    for (const auto& c : candidates) {
+        if (c.bn > 32 && n < c.bn) continue;
+        const long tiles = static_cast<long>((m + 127) / 128) * ((n + c.bn - 1) / c.bn);
         const long waves = (tiles + num_sms - 1) / num_sms;
-        const long cost = waves * (bn + 64);
-        if (best_cost < 0 || cost < best_cost) {
+        const double cost = static_cast<double>(waves) * c.tile_cost;
+        if (best_cost < 0.0 || cost < best_cost * 0.98) {  // a narrower tile must win by 2 % to be taken
             best_cost = cost;
-            best = bn;
+            best = c.bn;
         }
     }
     return best;
@@ -137,7 +140,11 @@ int dispatch_gemm(yan::GemmType type, yan::OutKind out_kind, yan::GemmArgs& a, i
     switch (block_n) {
         case 32: return yan::launch_gemm_bn32(type, out_kind, a, s);
         case 64: return yan::launch_gemm_bn64(type, out_kind, a, s);
+        case 96: return yan::launch_gemm_bn96(type, out_kind, a, s);
         case 128: return yan::launch_gemm_bn128(type, out_kind, a, s);
+        case 160: return yan::launch_gemm_bn160(type, out_kind, a, s);
+        case 192: return yan::launch_gemm_bn192(type, out_kind, a, s);
+        case 224: return yan::launch_gemm_bn224(type, out_kind, a, s);
         case 256: return yan::launch_gemm_bn256(type, out_kind, a, s);
         default: return yan::kBadArgument;
     }

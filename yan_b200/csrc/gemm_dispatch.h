@@ -11,12 +11,17 @@ enum class OutKind { BF16 = 0, F32 = 1, E4M3 = 2 };
 
 int launch_gemm_bn32(GemmType type, OutKind out, const GemmArgs& args, cudaStream_t stream);
 int launch_gemm_bn64(GemmType type, OutKind out, const GemmArgs& args, cudaStream_t stream);
+int launch_gemm_bn96(GemmType type, OutKind out, const GemmArgs& args, cudaStream_t stream);
 int launch_gemm_bn128(GemmType type, OutKind out, const GemmArgs& args, cudaStream_t stream);
+int launch_gemm_bn160(GemmType type, OutKind out, const GemmArgs& args, cudaStream_t stream);
+int launch_gemm_bn192(GemmType type, OutKind out, const GemmArgs& args, cudaStream_t stream);
+int launch_gemm_bn224(GemmType type, OutKind out, const GemmArgs& args, cudaStream_t stream);
 int launch_gemm_bn256(GemmType type, OutKind out, const GemmArgs& args, cudaStream_t stream);
 
-// Default pipeline depth per BLOCK_N: as many 128-wide k-block stages as fit in 227 KB next to the barriers.
+// Default pipeline depth per BLOCK_N: 128-wide k-block stages (16 KB of A + BLOCK_N * 128 bytes of B each) that fit
+// in 227 KB next to the barriers, at most 8.
 constexpr uint32_t default_num_stages(uint32_t block_n) {
-    return block_n == 256 ? 4 : block_n == 128 ? 6 : 8;
+    return block_n == 256 ? 4 : block_n >= 192 ? 5 : block_n == 160 ? 6 : block_n == 128 ? 6 : 8;
 }
 
 }  // namespace yan

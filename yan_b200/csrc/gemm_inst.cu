@@ -1,8 +1,8 @@
-// One instantiation unit of the FP8 GEMM per BLOCK_N (compile with -DYAN_BLOCK_N=32|64|128|256).
+// One instantiation unit of the FP8 GEMM per BLOCK_N (compile with -DYAN_BLOCK_N=32|64|96|128|160|192|224|256).
 #include "gemm_dispatch.h"
 
 #ifndef YAN_BLOCK_N
-#error "compile with -DYAN_BLOCK_N=<32|64|128|256>"
+#error "compile with -DYAN_BLOCK_N=<32|64|96|128|160|192|224|256>"
 #endif
 
 #define YAN_CAT_(a, b) a##b

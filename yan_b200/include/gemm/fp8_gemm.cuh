@@ -142,8 +142,10 @@ struct E4m3Out {
 
 template <uint32_t BLOCK_N, uint32_t kNumStages>
 struct GemmSmemLayout {
-    static constexpr uint32_t kNumTmemBufs = (BLOCK_N >= 256) ? 2 : 4;
-    static constexpr uint32_t kTmemCols = kNumTmemBufs * BLOCK_N;
+    static constexpr uint32_t kNumTmemBufs = (BLOCK_N > 128) ? 2 : 4;
+    static constexpr uint32_t kTmemColsUsed = kNumTmemBufs * BLOCK_N;
+    static constexpr uint32_t kTmemCols =  // allocations are powers of two
+        kTmemColsUsed <= 32 ? 32 : kTmemColsUsed <= 64 ? 64 : kTmemColsUsed <= 128 ? 128 : kTmemColsUsed <= 256 ? 256 : 512;
     static constexpr uint32_t SMEM_A_SIZE_PER_STAGE = kBlockM * kBlockK;
     static constexpr uint32_t SMEM_B_SIZE_PER_STAGE = BLOCK_N * kBlockK;
     static constexpr uint32_t kOffA = 0;
@@ -154,8 +156,7 @@ struct GemmSmemLayout {
     static constexpr uint32_t kOffAbort = kOffTmemSlot + 4;
     // +1024: the dynamic shared-memory base is re-aligned to 1024 bytes inside the kernel.
     static constexpr uint32_t kSmemSize = kOffAbort + 4 + 1024;
-    static_assert(kTmemCols == 32 || kTmemCols == 64 || kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512,
-                  "TMEM allocations are powers of two between 32 and 512 columns");
+    static_assert(kTmemColsUsed <= 512, "tensor memory has 512 columns");
     static_assert(BLOCK_N % 32 == 0 && BLOCK_N >= 32 && BLOCK_N <= 256, "UMMA M=128 needs N % 16 == 0, N <= 256");
 };
 
@@ -171,10 +172,19 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     static_assert(RegisterBudgetCheck<BLOCK_N>::ok);
     constexpr uint32_t kColsPerWG = BLOCK_N / kNumMathWGs;
     constexpr uint32_t kNumMathWarps = 4 * kNumMathWGs;
-    constexpr uint32_t kMaxChunk = (kNumMathWGs == 4) ? 16 : 32;  // 112 registers leave little room
-    constexpr uint32_t kChunk = kColsPerWG < kMaxChunk ? kColsPerWG : kMaxChunk;  // columns per tcgen05.ld
+    // Columns move TMEM -> registers in chunks of 32 (the fastest tcgen05.ld shape measured) plus, when BLOCK_N/2 is
+    // not a multiple of 32 (BLOCK_N = 224, 160, 96), one chunk of 16.
+    static_assert(kColsPerWG % 16 == 0, "a promotion warpgroup owns a multiple of 16 columns");
+    constexpr uint32_t kChunk = kColsPerWG < 32 ? kColsPerWG : 32;
     constexpr uint32_t kNumChunks = kColsPerWG / kChunk;
-    constexpr uint32_t kScaleDepth = (kNumMathWGs == 4) ? 2 : 4;
+    constexpr uint32_t kTailChunk = kColsPerWG - kNumChunks * kChunk;  // 0 or 16
+    static_assert(kTailChunk == 0 || kTailChunk == 16);
+    // A warpgroup's column range lies inside one 128-column scale block when it divides 128 or is a multiple of it
+    // starting on a block boundary (BLOCK_N = 32, 64, 128, 256).  Otherwise it can straddle one boundary, at a
+    // multiple of 16 columns: two B scales per k-block, chosen per group of 16 columns (the case the reference
+    // handles for BLOCK_N not dividing BLOCK_K, fp8_gemm.cuh:55-61,149-160).
+    constexpr bool kTwoScales = (128 % kColsPerWG != 0) && (kColsPerWG % 128 != 0);
+    constexpr uint32_t kScaleDepth = 4;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -315,13 +325,18 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
             const uint32_t sb_row = min(n_first / 128u, num_sb_rows - 1);
             const float* sa_ptr = p.scales_a + row;
             const float* sb_ptr = p.scales_b + (static_cast<size_t>(group) * num_sb_rows + sb_row) * num_k_blocks;
+            // two-scale case: groups of 16 columns from `hi_from` on belong to the next 128-column block
+            const uint32_t hi_from = kTwoScales ? (128u - n_first % 128u) / 16u : 0xFFFFu;
+            const float* sb_hi_ptr =
+                p.scales_b + (static_cast<size_t>(group) * num_sb_rows + min(sb_row + 1, num_sb_rows - 1)) * num_k_blocks;
 
             // Scales are prefetched kScaleDepth k-blocks ahead: one L2 round trip is longer than one k-block.
-            float sa_ring[kScaleDepth], sb_ring[kScaleDepth];
+            float sa_ring[kScaleDepth], sb_ring[kScaleDepth], sb_hi_ring[kTwoScales ? kScaleDepth : 1];
 #pragma unroll
             for (uint32_t i = 0; i < kScaleDepth; ++i) {
                 sa_ring[i] = (row_ok && i < num_k_blocks) ? __ldg(sa_ptr + static_cast<size_t>(i) * p.sa_ld) : 0.0f;
                 sb_ring[i] = (i < num_k_blocks) ? __ldg(sb_ptr + i) : 0.0f;
+                if constexpr (kTwoScales) sb_hi_ring[i] = (i < num_k_blocks) ? __ldg(sb_hi_ptr + i) : 0.0f;
             }
 #pragma unroll
             for (uint32_t j = 0; j < kColsPerWG; ++j) acc[j] = 0.0f;
@@ -332,9 +347,12 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
                     const uint32_t kb = kb0 + i;
                     if (!alive || kb >= num_k_blocks) continue;
                     const float scale = sa_ring[i] * sb_ring[i];
+                    float scale_hi = scale;
+                    if constexpr (kTwoScales) scale_hi = sa_ring[i] * sb_hi_ring[i];
                     if (kb + kScaleDepth < num_k_blocks) {
                         sa_ring[i] = row_ok ? __ldg(sa_ptr + static_cast<size_t>(kb + kScaleDepth) * p.sa_ld) : 0.0f;
                         sb_ring[i] = __ldg(sb_ptr + kb + kScaleDepth);
+                        if constexpr (kTwoScales) sb_hi_ring[i] = __ldg(sb_hi_ptr + kb + kScaleDepth);
                     }
                     const bool ok = detail::bounded_wait(tmem_full_barriers + buf, buf_phase, abort_flag, p, 4);
                     if (!__all_sync(0xffffffffu, ok)) {
@@ -344,26 +362,41 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
                     ptx::tcgen05_fence_after_thread_sync();
                     const uint32_t taddr = tmem_lane_base + buf * BLOCK_N;
 
-                    // Chunks of kChunk columns move TMEM -> registers.  The TMEM buffer is handed back as soon
-                    // as the last chunk has landed, before its FMAs.
+                    // The TMEM buffer is handed back as soon as the last chunk has landed, before its FMAs.
                     // Nothing is scheduled between a tcgen05.ld and its wait: FMAs issued while a load is
                     // outstanding were measured ~10x slower than after it (the load does not overlap with the
                     // issuing warp's own arithmetic), so a second landing buffer buys nothing.  Also measured and
                     // slower: postponing warpgroup 1's last chunk to its next k-block so that the two warps of
                     // a sub-partition alternate between loading and multiplying (1.93 vs 2.17 PFLOP/s on C4).
+                    auto release_buffer = [&]() {
+                        ptx::tcgen05_fence_before_thread_sync();
+                        __syncwarp();
+                        if (lane_idx == 0) ptx::mbar_arrive(tmem_empty_barriers + buf);
+                    };
+                    auto group_scale = [&](uint32_t group16) { return (kTwoScales && group16 >= hi_from) ? scale_hi : scale; };
 #pragma unroll
                     for (uint32_t c = 0; c < kNumChunks; ++c) {
                         uint32_t t[kChunk];
                         ptx::tmem_ld_32x32b<kChunk>(taddr + c * kChunk, t);
                         ptx::tmem_ld_wait<kChunk>(t);
-                        if (c + 1 == kNumChunks) {
-                            ptx::tcgen05_fence_before_thread_sync();
-                            __syncwarp();
-                            if (lane_idx == 0) ptx::mbar_arrive(tmem_empty_barriers + buf);
-                        }
+                        if (kTailChunk == 0 && c + 1 == kNumChunks) release_buffer();
 #pragma unroll
-                        for (uint32_t j = 0; j < kChunk; ++j)
-                            acc[c * kChunk + j] = fmaf(scale, __uint_as_float(t[j]), acc[c * kChunk + j]);
+                        for (uint32_t h = 0; h < kChunk / 16; ++h) {
+                            const float sc = group_scale((c * kChunk) / 16 + h);
+#pragma unroll
+                            for (uint32_t j = h * 16; j < h * 16 + 16; ++j)
+                                acc[c * kChunk + j] = fmaf(sc, __uint_as_float(t[j]), acc[c * kChunk + j]);
+                        }
+                    }
+                    if constexpr (kTailChunk != 0) {
+                        uint32_t t[16];
+                        ptx::tmem_ld_32x32b<16>(taddr + kNumChunks * kChunk, t);
+                        ptx::tmem_ld_wait<16>(t);
+                        release_buffer();
+                        const float sc = group_scale((kNumChunks * kChunk) / 16);
+#pragma unroll
+                        for (uint32_t j = 0; j < 16; ++j)
+                            acc[kNumChunks * kChunk + j] = fmaf(sc, __uint_as_float(t[j]), acc[kNumChunks * kChunk + j]);
                     }
                     if (++buf == kNumTmemBufs) {
                         buf = 0;

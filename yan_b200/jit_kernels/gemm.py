@@ -51,25 +51,29 @@ arg_defs = (('lhs', torch.float8_e4m3fn), ('lhs_scales', torch.float),
             ('out', torch.bfloat16), ('m', int),
             ('stream', torch.cuda.Stream), ('num_sms', int), ('smem_size', int))
 
-_DEFAULT_STAGES = {32: 8, 64: 8, 128: 6, 256: 4}
+_DEFAULT_STAGES = {32: 8, 64: 8, 96: 8, 128: 6, 160: 6, 192: 5, 224: 5, 256: 4}
 
 
 def get_smem_size(block_n: int, num_stages: int) -> int:
     """Dynamic shared memory of one CTA: stages x (A 128x128 + B BLOCK_Nx128 e4m3) + mbarriers +
     1024 bytes of alignment slack (GemmSmemLayout in include/gemm/fp8_gemm.cuh)."""
-    num_tmem_bufs = 2 if block_n >= 256 else 4
+    num_tmem_bufs = 2 if block_n > 128 else 4
     return num_stages * (128 * 128 + block_n * 128) + (2 * num_stages + 2 * num_tmem_bufs) * 8 + 8 + 1024
+
+
+# time of one tile relative to a 256-wide one (measured; see choose_block_n in csrc/capi.cu)
+_TILE_COST = {256: 1.000, 224: 0.985, 192: 0.869, 160: 0.823, 128: 0.672, 96: 0.62, 64: 0.50, 32: 0.42}
 
 
 def get_best_configs(m: int, n: int, k: int, num_sms: int) -> Tuple[int, int, int]:
     """(BLOCK_N, NUM_STAGES, smem_size) by the same wave model as the C library's default."""
     best, best_cost = 256, None
-    for bn in (256, 128, 64, 32):
+    for bn, tile_cost in _TILE_COST.items():
         if bn > 32 and n < bn:
             continue
         waves = ceil_div(ceil_div(m, 128) * ceil_div(n, bn), num_sms)
-        cost = waves * (bn + 64)
-        if best_cost is None or cost < best_cost:
+        cost = waves * tile_cost
+        if best_cost is None or cost < best_cost * 0.98:
             best, best_cost = bn, cost
     stages = _DEFAULT_STAGES[best]
     return best, stages, get_smem_size(best, stages)
@@ -122,7 +126,7 @@ def gemm_fp8_fp8_bf16_nt(lhs: Tuple[torch.Tensor, torch.Tensor], rhs: Tuple[torc
         args = (lhs_q, lhs_scales, rhs_q, rhs_scales, out, m, torch.cuda.current_stream(), num_sms, 0)
         if block_n == 0 and int(os.environ.get("YAN_FP8_GEMM_TUNE", "0")):
             # time every tile width that can fill the machine; the winner is remembered per (N, K, M bucket)
-            space = tuple({'BLOCK_N': bn, 'NUM_STAGES': _DEFAULT_STAGES[bn]} for bn in (256, 128, 64, 32) if bn <= n)
+            space = tuple({'BLOCK_N': bn, 'NUM_STAGES': _DEFAULT_STAGES[bn]} for bn in (256, 224, 192, 160, 128, 96, 64, 32) if bn <= n)
             keys = {'N': n, 'K': k, 'BLOCK_M': 128, 'M_BUCKET': ceil_div(m, 128)}
         else:
             bn = get_best_configs(m, n, k, num_sms)[0] if block_n == 0 else block_n
