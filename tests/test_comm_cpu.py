@@ -87,6 +87,25 @@ def _worker(rank: int, world: int, port: int, mode: str, results):
                                            gemm_fn=_oracle_gemm)
             ok = res is comm.buffer and comm.calls == [(0, m)]
             ok = ok and ref.rel_frobenius(res, ref.ref_gemm_k_split(lhs, rhs, world)) <= 2e-3
+        elif mode in ("peer_export_failure", "peer_open_failure"):
+            # One rank cannot export (or cannot map a peer's) buffer: every rank must raise, with that rank's message,
+            # and none may be left waiting in a collective.  The C calls are replaced by stand-ins; no GPU involved.
+            from yan_b200 import _lib
+            from yan_b200.comm import peer_memory
+
+            def fake_call(name, *args):
+                if name == "yan_b200_ipc_export" and mode == "peer_export_failure" and rank == 1:
+                    raise _lib.YanB200Error(name, 5, "collective library reported an error")
+                if name == "yan_b200_ipc_open" and mode == "peer_open_failure" and rank == 0:
+                    raise _lib.YanB200Error(name, 5, "collective library reported an error")
+
+            peer_memory._lib.call = fake_call
+            try:
+                peer_memory.PeerSharedTensor((64,), torch.uint8, device="cpu")
+                ok = False
+            except RuntimeError as e:
+                culprit = "rank 1" if mode == "peer_export_failure" else "rank 0 mapping rank 1"
+                ok = culprit in str(e) and not peer_memory._opened
         elif mode == "rank_failure":
             # A rank that raises before the collective: the survivor's allreduce must end with an error, not hang.
             if rank == 1:
@@ -124,6 +143,13 @@ def _run(mode: str, expect_all: bool = True):
 
 @pytest.mark.parametrize("mode", ["n_split", "k_split_f32", "k_split_bf16", "k_split_two_shot_host"])
 def test_sharded_gemm_world2_gloo(mode):
+    results, codes = _run(mode)
+    assert codes == [0, 0], codes
+    assert results == {0: True, 1: True}, results
+
+
+@pytest.mark.parametrize("mode", ["peer_export_failure", "peer_open_failure"])
+def test_peer_memory_setup_fails_on_every_rank_together(mode):
     results, codes = _run(mode)
     assert codes == [0, 0], codes
     assert results == {0: True, 1: True}, results

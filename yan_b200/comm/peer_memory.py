@@ -34,42 +34,58 @@ def slice_bounds(count: int, world: int, rank: int) -> Tuple[int, int]:
 class PeerSharedTensor:
     """`local` is this rank's tensor; `ptrs[r]` is the address of rank r's tensor in this process."""
 
-    def __init__(self, shape, dtype: torch.dtype, group: Optional[dist.ProcessGroup] = None):
+    def __init__(self, shape, dtype: torch.dtype, group: Optional[dist.ProcessGroup] = None, device: str = "cuda"):
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
-        self.local = torch.zeros(shape, dtype=dtype, device="cuda")
-        handle = (ctypes.c_ubyte * 64)()
-        offset = ctypes.c_ulonglong(0)
-        _lib.call("yan_b200_ipc_export", ctypes.c_void_p(self.local.data_ptr()), handle, ctypes.byref(offset))
-        mine = (os.getpid(), bytes(handle), int(offset.value), self.local.device.index)
+        self.local = torch.zeros(shape, dtype=dtype, device=device)  # `device` exists for host-side tests of the hand-shake
+        # Every step that can fail on one rank only is followed by an exchange of the outcome, so that all ranks raise
+        # together instead of one leaving the others inside a collective.
+        try:
+            handle = (ctypes.c_ubyte * 64)()
+            offset = ctypes.c_ulonglong(0)
+            _lib.call("yan_b200_ipc_export", ctypes.c_void_p(self.local.data_ptr()), handle, ctypes.byref(offset))
+            mine = (os.getpid(), bytes(handle), int(offset.value), None)
+        except Exception as e:  # noqa: BLE001 - reported to every rank below
+            mine = (os.getpid(), b"", 0, f"rank {self.rank}: {type(e).__name__}: {e}")
         everyone: list = [None] * self.world
         dist.all_gather_object(everyone, mine, group=group)
+        errors = [e[3] for e in everyone if e[3] is not None]
+        if errors:
+            raise RuntimeError("peer memory export failed: " + "; ".join(errors))
         self._keys: List[Tuple[int, bytes]] = []
         self.ptrs: List[int] = []
-        for r, (pid, h, off, _dev) in enumerate(everyone):
+        failure = None
+        for r, (pid, h, off, _err) in enumerate(everyone):
             if r == self.rank:
                 self.ptrs.append(self.local.data_ptr())
                 continue
             key = (pid, h)
-            if key not in _opened:
-                base = ctypes.c_void_p(0)
-                buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
-                _lib.call("yan_b200_ipc_open", buf, ctypes.byref(base))
-                _opened[key] = [int(base.value), 0]
-            _opened[key][1] += 1
-            self._keys.append(key)
-            self.ptrs.append(_opened[key][0] + off)
-        torch.cuda.synchronize()
+            try:
+                if key not in _opened:
+                    base = ctypes.c_void_p(0)
+                    buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                    _lib.call("yan_b200_ipc_open", buf, ctypes.byref(base))
+                    _opened[key] = [int(base.value), 0]
+                _opened[key][1] += 1
+                self._keys.append(key)
+                self.ptrs.append(_opened[key][0] + off)
+            except Exception as e:  # noqa: BLE001
+                failure = f"rank {self.rank} mapping rank {r}: {type(e).__name__}: {e}"
+                break
+        outcomes: list = [None] * self.world
+        dist.all_gather_object(outcomes, failure, group=group)
+        if any(o is not None for o in outcomes):
+            self._unmap()
+            raise RuntimeError("peer memory mapping failed: " + "; ".join(o for o in outcomes if o is not None))
+        if self.local.is_cuda:
+            torch.cuda.synchronize()
         dist.barrier(group=group)  # every rank has mapped every buffer (and zeroed its own) before anyone uses them
 
     def ptr_array(self):
         return (ctypes.c_void_p * self.world)(*self.ptrs)
 
-    def close(self) -> None:
-        """Unmaps the peers' buffers.  Collective: no rank may still be using this rank's buffer."""
-        torch.cuda.synchronize()
-        dist.barrier(group=self.group)
+    def _unmap(self) -> None:
         for key in self._keys:
             entry = _opened[key]
             entry[1] -= 1
@@ -77,6 +93,12 @@ class PeerSharedTensor:
                 _lib.call("yan_b200_ipc_close", ctypes.c_void_p(entry[0]))
                 del _opened[key]
         self._keys = []
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers.  Collective: no rank may still be using this rank's buffer."""
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        self._unmap()
 
 
 class MulticastSharedTensor:
