@@ -236,11 +236,18 @@ def bench_decode(m: int, peaks) -> dict:
         yan_b200.fp8_linear(a, rhs_list[i % sets], outs[i % sets], workspace=ws)
 
     t_linear = time_graph_replays(fn_linear, replays=20, launches_per_graph=sets)
+    # the same chain with the quantizer launched programmatically too (its launch overlaps the previous GEMM's tail)
+    yan_b200.set_programmatic_dependent_launch(True)
+    try:
+        t_linear_pdl = time_graph_replays(fn_linear, replays=20, launches_per_graph=sets)
+    finally:
+        yan_b200.set_programmatic_dependent_launch(False)
     algo_bytes = m * k + 4 * m * (k // 128) + n * k + 4 * (n // 128) * (k // 128) + 2 * m * n
     gbs = algo_bytes / t / 1e9
     return {"workload": f"C2 decode M={m} N={n} K={k}", "us": t * 1e6, "GB/s": gbs, "algorithmic_bytes": algo_bytes,
             "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "frac_of_nominal_8TBs": gbs / 8000.0,
             "fp8_linear_us (quantize + GEMM, bf16 in)": t_linear * 1e6,
+            "fp8_linear_us, quantizer launched programmatically too": t_linear_pdl * 1e6,
             "us_without_programmatic_launch": t_serial * 1e6, "GB/s_without_programmatic_launch": algo_bytes / t_serial / 1e9,
             "timing": f"CUDA graph of {sets} launches over {sets} distinct B/D sets (>= 2 x L2), 20 replays, "
                       "programmatic dependent launch between consecutive GEMMs"}

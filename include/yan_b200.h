@@ -214,6 +214,8 @@ void yan_b200_allreduce_bf16_in_switch(void* multicast, void* const* signals, in
  * previous kernel of the stream is still running; activations, scales of the activations and the output are
  * only touched after the previous kernel has completed.  Enable it only when `rhs` / `rhs_scales` are not
  * written by the kernel that precedes the GEMM in its stream (true for inference weights).  Default: off.
+ * While enabled, the quantizer inside yan_b200_fp8_linear_bf16(_static) is launched the same way: its launch overlaps
+ * the tail of the previous kernel of the stream, and it waits for that kernel before it reads or writes anything.
  * No reference counterpart (the reference launches every kernel with plain <<<>>>, e.g.
  * yan/include/gemm/cute_gemm.cuh:373).
  */

@@ -198,6 +198,36 @@ def test_fp8_linear_matches_two_step(cuda_lib):
     _check(out.cpu(), ref.ref_gemm(lhs, rhs), "fp8_linear")
 
 
+@pytest.mark.parametrize("m", [16, 48])
+def test_chained_fp8_linear_with_programmatic_launch(cuda_lib, m):
+    """Six dependent decode layers (each layer's output is the next one's input, one shared workspace) with every
+    kernel launched programmatically: the quantizer may be resident while the GEMM before it still runs, the GEMM
+    streams weights while its quantizer runs.  The results must equal the serially launched chain bit for bit."""
+    import yan_b200
+    a, b = ref.make_inputs(m, 2048, 2048, seed=21)
+    rhs = tuple(t.cuda() for t in ref.per_block_cast_to_fp8(b))
+    ws = torch.empty(yan_b200.fp8_linear_workspace_bytes(m, 2048), dtype=torch.uint8, device="cuda")
+
+    def chain():
+        x, outs = a.cuda(), []
+        for _ in range(6):
+            x = yan_b200.fp8_linear(x, rhs, torch.empty(m, 2048, dtype=torch.bfloat16, device="cuda"), workspace=ws)
+            outs.append(x)
+        torch.cuda.synchronize()
+        return outs
+
+    serial = chain()
+    yan_b200.set_programmatic_dependent_launch(True)
+    try:
+        overlapped = chain()
+    finally:
+        yan_b200.set_programmatic_dependent_launch(False)
+    assert yan_b200.read_device_status() == 0
+    assert all(torch.equal(s, o) for s, o in zip(serial, overlapped))
+    lhs = ref.per_token_cast_to_fp8(a)
+    _check(serial[0].cpu(), ref.ref_gemm(lhs, tuple(t.cpu() for t in rhs)), "first layer")
+
+
 def test_gemm_rejects_bad_arguments(cuda_lib):
     import ctypes
     from yan_b200 import _lib

@@ -321,7 +321,8 @@ YAN_EXPORT void yan_b200_fp8_linear_bf16(const void* a, const void* rhs, const v
         return set_rc(return_code, yan::kWorkspaceTooSmall);
     uint8_t* q = static_cast<uint8_t*>(workspace);
     float* scales = reinterpret_cast<float*>(q + yan::align_up(static_cast<size_t>(m) * k, static_cast<size_t>(256)));
-    int rc = yan::launch_per_token_cast_to_fp8(a, q, scales, m, k, k, m, static_cast<cudaStream_t>(stream));
+    int rc = yan::launch_per_token_cast_to_fp8(a, q, scales, m, k, k, m, static_cast<cudaStream_t>(stream),
+                                               g_programmatic_launch != 0);
     if (rc != yan::kOk) return set_rc(return_code, rc);
     set_rc(return_code, gemm_after_quantizer(q, scales, rhs, rhs_scales, out, m, n, k, ldd, stream, num_sms, block_n));
 }
@@ -337,7 +338,8 @@ YAN_EXPORT void yan_b200_fp8_linear_bf16_static(const void* a, const void* rhs, 
     if (scratch == nullptr) return set_rc(return_code, yan::kLaunchFailed);
     uint8_t* q = scratch;
     float* scales = reinterpret_cast<float*>(scratch + kStaticScratchQBytes);
-    const int rc = yan::launch_per_token_cast_to_fp8(a, q, scales, m, k, k, m, static_cast<cudaStream_t>(stream));
+    const int rc = yan::launch_per_token_cast_to_fp8(a, q, scales, m, k, k, m, static_cast<cudaStream_t>(stream),
+                                                     g_programmatic_launch != 0);
     if (rc != yan::kOk) return set_rc(return_code, rc);
     set_rc(return_code, gemm_after_quantizer(q, scales, rhs, rhs_scales, out, m, n, k, ldd, stream, num_sms, block_n));
 }

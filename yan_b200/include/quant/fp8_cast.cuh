@@ -66,6 +66,10 @@ __global__ void __launch_bounds__(256) per_token_cast_to_fp8_kernel(const __nv_b
     // A GEMM launched behind this kernel with programmatic stream serialization may start its weight loads now;
     // it waits for this grid to complete before it touches the quantized activations.  No effect otherwise.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // When this kernel itself was launched with programmatic stream serialization its CTAs may be resident before the
+    // kernel that produces x has finished: wait for it (and for the previous readers of q / scales) here.  No effect
+    // for an ordinary launch.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const uint32_t hw = threadIdx.x / 16, l = threadIdx.x % 16;
     const uint32_t row0 = blockIdx.y * kRows, kb0 = blockIdx.x * kGroups;
@@ -135,23 +139,38 @@ __global__ void __launch_bounds__(256) per_block_cast_to_fp8_kernel(const __nv_b
 }
 
 // Host launchers.  Return a ReturnCode.
+// programmatic: launch with programmatic stream serialization, so that the launch latency overlaps the tail of the
+// kernel before it in the stream (the kernel waits for that kernel before it reads or writes anything).
 inline int launch_per_token_cast_to_fp8(const void* x, void* q, float* scales, uint32_t m, uint32_t k, uint32_t x_ld,
-                                        uint32_t sa_ld, cudaStream_t stream) {
+                                        uint32_t sa_ld, cudaStream_t stream, bool programmatic = false) {
     if (x == nullptr || q == nullptr || scales == nullptr || m == 0 || k == 0 || k % 128 != 0) return kBadArgument;
     if (x_ld < k || x_ld % 8 != 0 || sa_ld < m) return kBadArgument;
     if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || reinterpret_cast<uintptr_t>(q) % 8 != 0) return kBadArgument;
     const uint32_t num_kb = k / 128;
     const auto* xp = reinterpret_cast<const __nv_bfloat16*>(x);
     auto* qp = reinterpret_cast<uint8_t*>(q);
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
+    cudaError_t e;
     if (m >= 1024) {
-        dim3 grid(ceil_div(num_kb, 4u), ceil_div(m, 32u));
-        if (grid.y > 65535) return kBadArgument;
-        per_token_cast_to_fp8_kernel<32><<<grid, 256, 0, stream>>>(xp, qp, scales, m, k, x_ld, sa_ld);
+        cfg.gridDim = dim3(ceil_div(num_kb, 4u), ceil_div(m, 32u));
+        if (cfg.gridDim.y > 65535) return kBadArgument;
+        e = cudaLaunchKernelEx(&cfg, per_token_cast_to_fp8_kernel<32>, xp, qp, scales, m, k, x_ld, sa_ld);
     } else {
-        dim3 grid(ceil_div(num_kb, 4u), ceil_div(m, 8u));
-        per_token_cast_to_fp8_kernel<8><<<grid, 256, 0, stream>>>(xp, qp, scales, m, k, x_ld, sa_ld);
+        cfg.gridDim = dim3(ceil_div(num_kb, 4u), ceil_div(m, 8u));
+        e = cudaLaunchKernelEx(&cfg, per_token_cast_to_fp8_kernel<8>, xp, qp, scales, m, k, x_ld, sa_ld);
     }
-    return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return kLaunchFailed;
+    }
+    return kOk;
 }
 
 inline int launch_per_block_cast_to_fp8(const void* w, void* q, float* scales, uint32_t n, uint32_t k,

@@ -266,7 +266,8 @@ def fp8_linear_workspace_bytes(m: int, k: int) -> int:
 
 def set_programmatic_dependent_launch(enabled: bool) -> None:
     """Lets the M <= 64 weight-streaming kernel start fetching weights while the previous kernel of the stream is
-    still running (programmatic dependent launch).  Only valid when the weights are not produced by that kernel."""
+    still running (programmatic dependent launch), and lets the quantizer inside fp8_linear be launched over the tail of
+    the kernel before it.  Only valid when the weights are not produced by the kernel that precedes a GEMM."""
     _lib.lib().yan_b200_set_programmatic_dependent_launch(int(bool(enabled)))
 
 
