@@ -17,8 +17,8 @@
 //     touches activations or the output after it; with the launch attribute set (see the host launcher) the
 //     weight loads of GEMM i+1 may start while GEMM i finishes.  Weights must therefore not be produced by the
 //     kernel that precedes the GEMM in the stream when that attribute is used;
-//   * the second CTA of a pair sends its fp32 partial through distributed shared memory (st.shared::cluster),
-//     the first adds its own and writes bf16.  No multicast, no remote global memory.  (Measured alternatives,
+//   * the second CTA of a pair sends its fp32 partial through distributed shared memory (16-byte st.shared::cluster),
+//     the first adds its own, transposes the bf16 tile through shared memory and writes it with 16-byte stores.  No multicast, no remote global memory.  (Measured alternatives,
 //     all slower end to end: a 4-CTA cluster with bulk-copy exchange -- the partial sums then cross the
 //     SM-to-SM network at about 2 TB/s for the whole chip, a third of the weight bytes again at M = 64 -- and
 //     one-way mbarrier hand-shakes instead of the two cluster barriers: a remote arrive costs ~300 ns.)
@@ -38,16 +38,21 @@ constexpr uint32_t kSmallMThreads = 160;   // warps 0-3: promotion (TMEM lane qu
 constexpr uint32_t kSmallMMaxKBlocks = 32;  // k-blocks per CTA
 
 struct SmallMSmem {
-    uint32_t off_w, off_x, off_scales, off_barriers, off_tmem_slot, off_abort, total;
+    uint32_t off_w, off_x, off_scales, off_stage, off_barriers, off_tmem_slot, off_abort, total;
 };
+
+// One weight row's partial sums in the exchange buffer: m_pad floats plus 4 of padding, so that the 16-byte accesses of
+// a warp (one row per lane) fall on all 32 banks.
+__host__ __device__ constexpr uint32_t small_m_exchange_row_bytes(uint32_t m_pad) { return (m_pad + 4u) * 4u; }
 
 __host__ __device__ inline SmallMSmem small_m_smem_layout(uint32_t m_pad, uint32_t kbh) {
     SmallMSmem s;
-    s.off_w = 0;  // kbh x [128 x 128 B] weight tiles; later the exchange buffer [m_pad][128] fp32
-    const uint32_t w_bytes = kbh * 16384u, exchange_bytes = m_pad * 128u * 4u;
+    s.off_w = 0;  // kbh x [128 x 128 B] weight tiles; later the exchange buffer [128 weight rows][m_pad + 4] fp32
+    const uint32_t w_bytes = kbh * 16384u, exchange_bytes = 128u * small_m_exchange_row_bytes(m_pad);
     s.off_x = s.off_w + (w_bytes > exchange_bytes ? w_bytes : exchange_bytes);  // kbh x [m_pad x 128 B] activation tiles
     s.off_scales = s.off_x + kbh * m_pad * 128u;  // kbh x m_pad floats: sA[m,kb] * sB[kb]
-    s.off_barriers = align_up(s.off_scales + kbh * m_pad * 4u, 8u);
+    s.off_stage = align_up(s.off_scales + kbh * m_pad * 4u, 16u);  // [m_pad][128] bf16: the output tile, row-major
+    s.off_barriers = align_up(s.off_stage + m_pad * 256u, 8u);
     s.off_tmem_slot = s.off_barriers + 2 * kSmallMMaxKBlocks * 8u;  // full[kb] and done[kb]
     s.off_abort = s.off_tmem_slot + 4;
     s.total = s.off_abort + 4 + 1024;
@@ -80,6 +85,15 @@ __device__ __forceinline__ float ld_shared_f32(uint32_t addr) {
 }
 __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void st_cluster_v4_f32(uint32_t addr, float a, float b, float c, float d) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+                 : "memory");
+}
+__device__ __forceinline__ float4 ld_shared_v4_f32(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
 }
 }  // namespace ptx
 
@@ -198,28 +212,47 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kSmallMThreads, 1)
     }
 
     // Both CTAs of the pair are past their MMAs and TMEM reads: the weight tiles of CTA 0 are dead and become
-    // the landing area for CTA 1's partial sums.
+    // the landing area for CTA 1's partial sums, one padded row of M_PAD floats per weight row (= per thread), so that
+    // both sides move 16 bytes per instruction.
     ptx::cluster_arrive();
     ptx::cluster_wait();
-    float* exchange = reinterpret_cast<float*>(smem + L.off_w);  // [M_PAD][128]
+    constexpr uint32_t kRowBytes = small_m_exchange_row_bytes(M_PAD);
     const uint32_t n_in_tile = warp_idx * 32 + lane_idx;
+    const uint32_t exchange = ptx::smem_u32(smem + L.off_w) + n_in_tile * kRowBytes;
     if (warp_idx < 4 && cta_rank == 1) {
-        const uint32_t remote = ptx::map_to_cta(ptx::smem_u32(exchange), 0);
+        const uint32_t remote = ptx::map_to_cta(exchange, 0);
 #pragma unroll
-        for (uint32_t m = 0; m < M_PAD; ++m) ptx::st_cluster_f32(remote + (m * 128u + n_in_tile) * 4u, acc[m]);
+        for (uint32_t m = 0; m < M_PAD; m += 4)
+            ptx::st_cluster_v4_f32(remote + m * 4u, acc[m], acc[m + 1], acc[m + 2], acc[m + 3]);
     }
     ptx::cluster_arrive();
     ptx::cluster_wait();
     if (warp_idx < 4 && cta_rank == 0 && alive && *abort_flag == 0) {
-        // Two phases, so that no global store sits between the shared-memory loads (with stores in the loop the
-        // compiler keeps load(m+1) behind store(m) and every row pays a full shared-memory latency).
-        const uint32_t ex = ptx::smem_u32(exchange) + n_in_tile * 4u;
 #pragma unroll
-        for (uint32_t m = 0; m < M_PAD; ++m) acc[m] += ptx::ld_shared_f32(ex + m * 512u);
-        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + n_block * 128u + n_in_tile;
+        for (uint32_t m = 0; m < M_PAD; m += 4) {
+            const float4 v = ptx::ld_shared_v4_f32(exchange + m * 4u);
+            acc[m] += v.x, acc[m + 1] += v.y, acc[m + 2] += v.z, acc[m + 3] += v.w;
+        }
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + n_block * 128u;
+        const bool vector_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (p.ldd % 8 == 0);
+        if (vector_ok) {
+            // Transpose through shared memory: [m][128 weight rows] bf16, then 16-byte global stores (a thread-per-
+            // weight-row store would write 2 bytes per lane and M_PAD instructions per thread).
+            __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(smem + L.off_stage);
 #pragma unroll
-        for (uint32_t m = 0; m < M_PAD; ++m)
-            if (m < p.shape_m) out[static_cast<size_t>(m) * p.ldd] = __float2bfloat16_rn(acc[m]);
+            for (uint32_t m = 0; m < M_PAD; ++m) stage[m * 128u + n_in_tile] = __float2bfloat16_rn(acc[m]);
+            ptx::named_barrier_sync(1, 128);
+            for (uint32_t c = threadIdx.x; c < M_PAD * 16u; c += 128) {
+                const uint32_t m = c / 16u, part = c % 16u;
+                if (m < p.shape_m)
+                    *reinterpret_cast<uint4*>(out + static_cast<size_t>(m) * p.ldd + part * 8u) =
+                        *reinterpret_cast<const uint4*>(stage + m * 128u + part * 8u);
+            }
+        } else {
+#pragma unroll
+            for (uint32_t m = 0; m < M_PAD; ++m)
+                if (m < p.shape_m) out[static_cast<size_t>(m) * p.ldd + n_in_tile] = __float2bfloat16_rn(acc[m]);
+        }
     }
 
     ptx::tcgen05_fence_before_thread_sync();
