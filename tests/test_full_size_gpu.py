@@ -78,3 +78,20 @@ def test_full_size_blocks_and_properties(cuda_lib, name, m, n, k):
     diff = (total.float() - d.float())
     fro = float(diff.norm() / d.float().norm())
     assert fro <= REL_FRO_TOL, f"{name}: full-K vs split-K rel Frobenius {fro:.2e}"
+
+
+def test_tile_widths_agree_bit_for_bit_at_full_size(cuda_lib):
+    """Every tile width adds the same scaled k-block products in the same order, so the C4 shard of an 8-GPU job must
+    come out identical from the 256-wide tiles and from the 224-wide ones (two B scales per warpgroup, 16-column tail
+    chunk, last tile partly beyond N for 192)."""
+    import yan_b200
+    m, n, k = 8192, 3584, 8192
+    lhs, rhs = _device_operands(m, n, k, seed=11)
+    want = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    yan_b200.gemm_fp8_fp8_bf16_nt(lhs, rhs, want, block_n=256)
+    for block_n in (224, 192, 160, 128):
+        got = torch.empty_like(want)
+        yan_b200.gemm_fp8_fp8_bf16_nt(lhs, rhs, got, block_n=block_n)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), f"block_n={block_n}"
+    assert yan_b200.read_device_status() == 0

@@ -83,7 +83,7 @@ inline void set_rc(int* rc, int v) {
 }
 
 // Picks BLOCK_N by a wave model: cost = waves * (time of one tile relative to a 256-wide one).  The relative tile
-// times are measured (M = 8192, N = 28672, K = 8192, time * SMs / tiles): the promotion of a k-block has a large fixed
+// times are measured (time / waves on M = 8192, K = 8192 with N = 3584 and 28672): the promotion of a k-block has a large fixed
 // part, so a narrower tile is far from proportionally cheaper, and the widths whose half does not divide 128 pay for a
 // second B scale and a 16-column tail chunk.  Large problems therefore get 256; narrower tiles win when they fill the
 // machine better (few tiles, or a last wave of 256-wide tiles that is nearly empty).
