@@ -125,7 +125,8 @@ int dispatch_gemm(yan::GemmType type, yan::OutKind out_kind, yan::GemmArgs& a, i
         cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
         const bool programmatic = g_programmatic_launch != 0 || after_own_quantizer;
         if (block_n == 2) {
-            if (!yan::stacked_k_supported(a.m, a.n, a.k, max_smem)) return yan::kBadArgument;
+            if (!yan::stacked_k_supported(a.m, a.n, a.k, max_smem) && !yan::stacked_k_ring_supported(a.m, a.n, a.k, max_smem))
+                return yan::kBadArgument;
             return yan::launch_fp8_gemm_stacked_k(a, s, programmatic);
         }
         if (want_auto) {
