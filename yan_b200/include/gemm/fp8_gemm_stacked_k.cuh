@@ -207,18 +207,19 @@ __global__ void __launch_bounds__(kStackedThreads, 2)
 //   warps 0-3: promotion; warp 4: sixteen producer lanes, lane = (slot, k-quarter); warp 5: TMEM + MMA issuer.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr uint32_t kRingThreads = 192;
-constexpr uint32_t kRingSlots = 4;
 constexpr uint32_t kRingMaxSteps = 32;
+// Slots per CTA: 4 (96 KB, two CTAs per SM) when the grid is larger than the GPU, 8 (192 KB, all 512 TMEM columns)
+// when every CTA has an SM to itself anyway (N/32 <= number of SMs), which doubles the bytes a CTA keeps in flight.
 
 struct StackedRingSmem {
     uint32_t off_w, off_x, off_scales, off_reduce, off_barriers, off_tmem_slot, off_abort, total;
 };
 
-__host__ __device__ inline StackedRingSmem stacked_k_ring_smem_layout(uint32_t steps) {
+__host__ __device__ inline StackedRingSmem stacked_k_ring_smem_layout(uint32_t steps, uint32_t kRingSlots) {
     constexpr uint32_t m_pad = 16;
     StackedRingSmem s;
-    s.off_w = 0;                                                   // 4 slots x [128 x 128 B]
-    s.off_x = s.off_w + kRingSlots * 16384u;                       // 4 slots x [4*16 x 128 B]
+    s.off_w = 0;                                                   // slots x [128 x 128 B]
+    s.off_x = s.off_w + kRingSlots * 16384u;                       // slots x [4*16 x 128 B]
     s.off_scales = s.off_x + kRingSlots * kStackFactor * m_pad * 128u;  // [4][steps][16] floats
     s.off_reduce = s.off_scales + kStackFactor * steps * m_pad * 4u;    // [4][16][32] floats
     s.off_barriers = align_up(s.off_reduce + kStackFactor * m_pad * kStackedRows * 4u, 8u);
@@ -228,20 +229,22 @@ __host__ __device__ inline StackedRingSmem stacked_k_ring_smem_layout(uint32_t s
     return s;
 }
 
-__global__ void __launch_bounds__(kRingThreads, 2)
+template <uint32_t kRingSlots>
+__global__ void __launch_bounds__(kRingThreads, kRingSlots == 4 ? 2 : 1)
     fp8_gemm_stacked_k_ring_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tensor_map_w,
                                    const __grid_constant__ CUtensorMap tensor_map_x) {
 #if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ >= 1000)
     constexpr uint32_t M_PAD = 16;
     constexpr uint32_t kMmaN = kStackFactor * M_PAD;  // 64
     constexpr uint32_t kStepBytes = 16384u + kMmaN * 128u;
-    constexpr uint32_t kTmemCols = kRingSlots * kMmaN;  // 256
+    constexpr uint32_t kTmemCols = kRingSlots * kMmaN;  // 256 or 512
+    static_assert(kRingSlots == 4 || kRingSlots == 8, "one producer lane per (slot, k-quarter): at most 8 slots");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
 
     const uint32_t num_k_blocks = p.shape_k / kBlockK;
     const uint32_t steps = num_k_blocks / kStackFactor;
-    const StackedRingSmem L = stacked_k_ring_smem_layout(steps);
+    const StackedRingSmem L = stacked_k_ring_smem_layout(steps, kRingSlots);
     uint64_t* full_barriers = reinterpret_cast<uint64_t*>(smem + L.off_barriers);
     uint64_t* done_barriers = full_barriers + kRingSlots;
     uint64_t* tmem_empty_barriers = done_barriers + kRingSlots;
@@ -276,7 +279,7 @@ __global__ void __launch_bounds__(kRingThreads, 2)
     if (warp_idx == 4) {
         if (lane_idx < kRingSlots * kStackFactor) {
             const uint32_t r = lane_idx / kStackFactor, q = lane_idx % kStackFactor;
-            const uint32_t group_mask = 0xFu << (r * kStackFactor);
+            const uint32_t group_mask = 0xFu << (r * kStackFactor);  // the four lanes of slot r
             uint8_t* w_dst = smem + L.off_w + r * 16384u + q * (kStackedRows * 128u);
             uint8_t* x_dst = smem + L.off_x + r * (kMmaN * 128u) + q * (M_PAD * 128u);
             // first fill: weights before the grid dependency (they are parameters), activations after it
@@ -405,8 +408,34 @@ __global__ void __launch_bounds__(kRingThreads, 2)
 inline bool stacked_k_ring_supported(uint32_t m, uint32_t n, uint32_t k, int max_smem) {
     if (m == 0 || m > 16 || n % kStackedRows != 0 || k % (kBlockK * kStackFactor) != 0) return false;
     const uint32_t steps = k / (kBlockK * kStackFactor);
-    if (steps <= kRingSlots || steps > kRingMaxSteps) return false;  // up to four steps need no ring
-    return stacked_k_ring_smem_layout(steps).total <= static_cast<uint32_t>(max_smem);
+    if (steps <= 4 || steps > kRingMaxSteps) return false;  // up to four steps need no ring
+    return stacked_k_ring_smem_layout(steps, 4).total <= static_cast<uint32_t>(max_smem);
+}
+
+template <uint32_t kRingSlots>
+inline int launch_stacked_k_ring_instance(const GemmParams& p, const CUtensorMap& map_w, const CUtensorMap& map_x,
+                                          uint32_t steps, uint32_t grid, cudaStream_t stream, bool programmatic) {
+    auto kernel = fp8_gemm_stacked_k_ring_kernel<kRingSlots>;
+    const uint32_t smem_ring = stacked_k_ring_smem_layout(steps, kRingSlots).total;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_ring) != cudaSuccess) {
+        cudaGetLastError();
+        return kSmemTooLarge;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kRingThreads);
+    cfg.dynamicSmemBytes = smem_ring;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, kernel, p, map_w, map_x) != cudaSuccess) {
+        cudaGetLastError();
+        return kLaunchFailed;
+    }
+    return kOk;
 }
 
 inline bool stacked_k_supported(uint32_t m, uint32_t n, uint32_t k, int max_smem) {
@@ -489,27 +518,12 @@ inline int launch_fp8_gemm_stacked_k(const GemmArgs& a, cudaStream_t stream, boo
     p.timeout_ns = a.timeout_ns;
     const uint32_t grid = a.n / kStackedRows;
     if (ring) {
-        const uint32_t smem_ring = stacked_k_ring_smem_layout(steps).total;
-        if (cudaFuncSetAttribute(fp8_gemm_stacked_k_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 smem_ring) != cudaSuccess) {
-            cudaGetLastError();
-            return kSmemTooLarge;
-        }
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(grid);
-        cfg.blockDim = dim3(kRingThreads);
-        cfg.dynamicSmemBytes = smem_ring;
-        cfg.stream = stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = programmatic ? 1 : 0;
-        if (cudaLaunchKernelEx(&cfg, fp8_gemm_stacked_k_ring_kernel, p, map_w, map_x) != cudaSuccess) {
-            cudaGetLastError();
-            return kLaunchFailed;
-        }
-        return kOk;
+        int sm_count = 0;
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+        const bool alone_on_sm = grid <= static_cast<uint32_t>(sm_count) && steps > 4 &&
+                                 stacked_k_ring_smem_layout(steps, 8).total <= static_cast<uint32_t>(max_smem);
+        if (alone_on_sm) return launch_stacked_k_ring_instance<8>(p, map_w, map_x, steps, grid, stream, programmatic);
+        return launch_stacked_k_ring_instance<4>(p, map_w, map_x, steps, grid, stream, programmatic);
     }
     const uint32_t smem_bytes = stacked_k_smem_layout(m_pad, steps).total;
     if (m_pad == 16) return launch_stacked_k_instance<16>(p, map_w, map_x, smem_bytes, grid, stream, programmatic);
