@@ -321,9 +321,9 @@ __global__ void __launch_bounds__(kRingThreads, kRingSlots == 4 ? 2 : 1)
             s_scales[i] = sa * __ldg(sb_ptr + qs);
         }
     }
-    // TMEM address and scales become visible to the MMA and promotion roles.  The producer lanes may still be in
-    // their refill loop: they join this barrier only after their last load, which the other roles' progress does
-    // not depend on... so the barrier below is among warps 0-3 and 5 only (160 threads + 32).
+    // TMEM address and scales become visible to the MMA and promotion roles.  The producer lanes are in their refill
+    // loop until the last load has gone out, and that loop needs the other roles to make progress, so the barrier
+    // below is among warps 0-3 and 5 only (128 + 32 = 160 threads); warp 4 joins the others at the end of the kernel.
     ptx::tcgen05_fence_before_thread_sync();
     if (warp_idx != 4) ptx::named_barrier_sync(2, 160);
     ptx::tcgen05_fence_after_thread_sync();
