@@ -130,9 +130,10 @@ int dispatch_gemm(yan::GemmType type, yan::OutKind out_kind, yan::GemmArgs& a, i
             return yan::launch_fp8_gemm_stacked_k(a, s, programmatic);
         }
         if (want_auto) {
-            int max_smem_sm = 0;
+            int max_smem_sm = 0, sm_count = 0;
             cudaDeviceGetAttribute(&max_smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
-            if (yan::stacked_k_preferred(a.m, a.n, a.k, max_smem, max_smem_sm))
+            cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+            if (yan::stacked_k_preferred(a.m, a.n, a.k, max_smem, max_smem_sm, sm_count))
                 return yan::launch_fp8_gemm_stacked_k(a, s, programmatic);
         }
         if (yan::small_m_supported(a.m, a.n, a.k, max_smem)) return yan::launch_fp8_gemm_small_m(a, s, programmatic);

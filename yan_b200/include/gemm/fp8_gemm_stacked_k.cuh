@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(kStackedThreads, 2)
 // Long K (more than four steps, K > 2048): the same kernel with its step buffers recycled.  Four step slots of shared
 // memory (96 KB: still two CTAs per SM) and four accumulator slots of tensor memory rotate: the loads of step s + 4 go
 // out as soon as the MMAs of step s are complete, the MMAs of step s + 4 wait until the promotion warps have read the
-// accumulator of step s.  Four steps per CTA stay in flight for the whole K loop.  M <= 16 only.
+// accumulator of step s.  Four steps per CTA stay in flight for the whole K loop.  M <= 32 (M_PAD 16 or 32).
 //   warps 0-3: promotion; warp 4: sixteen producer lanes, lane = (slot, k-quarter); warp 5: TMEM + MMA issuer.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr uint32_t kRingThreads = 192;
@@ -215,13 +215,13 @@ struct StackedRingSmem {
     uint32_t off_w, off_x, off_scales, off_reduce, off_barriers, off_tmem_slot, off_abort, total;
 };
 
-__host__ __device__ inline StackedRingSmem stacked_k_ring_smem_layout(uint32_t steps, uint32_t kRingSlots) {
-    constexpr uint32_t m_pad = 16;
+__host__ __device__ inline StackedRingSmem stacked_k_ring_smem_layout(uint32_t m_pad, uint32_t steps,
+                                                                      uint32_t kRingSlots) {
     StackedRingSmem s;
     s.off_w = 0;                                                   // slots x [128 x 128 B]
-    s.off_x = s.off_w + kRingSlots * 16384u;                       // slots x [4*16 x 128 B]
-    s.off_scales = s.off_x + kRingSlots * kStackFactor * m_pad * 128u;  // [4][steps][16] floats
-    s.off_reduce = s.off_scales + kStackFactor * steps * m_pad * 4u;    // [4][16][32] floats
+    s.off_x = s.off_w + kRingSlots * 16384u;                       // slots x [4*m_pad x 128 B]
+    s.off_scales = s.off_x + kRingSlots * kStackFactor * m_pad * 128u;  // [4][steps][m_pad] floats
+    s.off_reduce = s.off_scales + kStackFactor * steps * m_pad * 4u;    // [4][m_pad][32] floats
     s.off_barriers = align_up(s.off_reduce + kStackFactor * m_pad * kStackedRows * 4u, 8u);
     s.off_tmem_slot = s.off_barriers + 3 * kRingSlots * 8u;  // full, done, tmem_empty per slot
     s.off_abort = s.off_tmem_slot + 4;
@@ -229,22 +229,23 @@ __host__ __device__ inline StackedRingSmem stacked_k_ring_smem_layout(uint32_t s
     return s;
 }
 
-template <uint32_t kRingSlots>
-__global__ void __launch_bounds__(kRingThreads, kRingSlots == 4 ? 2 : 1)
+template <uint32_t M_PAD, uint32_t kRingSlots>
+__global__ void __launch_bounds__(kRingThreads, (M_PAD == 16 && kRingSlots == 4) ? 2 : 1)
     fp8_gemm_stacked_k_ring_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tensor_map_w,
                                    const __grid_constant__ CUtensorMap tensor_map_x) {
 #if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ >= 1000)
-    constexpr uint32_t M_PAD = 16;
-    constexpr uint32_t kMmaN = kStackFactor * M_PAD;  // 64
+    constexpr uint32_t kMmaN = kStackFactor * M_PAD;  // 64 or 128
     constexpr uint32_t kStepBytes = 16384u + kMmaN * 128u;
     constexpr uint32_t kTmemCols = kRingSlots * kMmaN;  // 256 or 512
+    static_assert(M_PAD == 16 || M_PAD == 32, "activation rows are padded to 16 or 32");
     static_assert(kRingSlots == 4 || kRingSlots == 8, "one producer lane per (slot, k-quarter): at most 8 slots");
+    static_assert(kTmemCols <= 512, "tensor memory has 512 columns");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
 
     const uint32_t num_k_blocks = p.shape_k / kBlockK;
     const uint32_t steps = num_k_blocks / kStackFactor;
-    const StackedRingSmem L = stacked_k_ring_smem_layout(steps, kRingSlots);
+    const StackedRingSmem L = stacked_k_ring_smem_layout(M_PAD, steps, kRingSlots);
     uint64_t* full_barriers = reinterpret_cast<uint64_t*>(smem + L.off_barriers);
     uint64_t* done_barriers = full_barriers + kRingSlots;
     uint64_t* tmem_empty_barriers = done_barriers + kRingSlots;
@@ -406,17 +407,17 @@ __global__ void __launch_bounds__(kRingThreads, kRingSlots == 4 ? 2 : 1)
 }
 
 inline bool stacked_k_ring_supported(uint32_t m, uint32_t n, uint32_t k, int max_smem) {
-    if (m == 0 || m > 16 || n % kStackedRows != 0 || k % (kBlockK * kStackFactor) != 0) return false;
+    if (m == 0 || m > 32 || n % kStackedRows != 0 || k % (kBlockK * kStackFactor) != 0) return false;
     const uint32_t steps = k / (kBlockK * kStackFactor);
     if (steps <= 4 || steps > kRingMaxSteps) return false;  // up to four steps need no ring
-    return stacked_k_ring_smem_layout(steps, 4).total <= static_cast<uint32_t>(max_smem);
+    return stacked_k_ring_smem_layout(m <= 16 ? 16 : 32, steps, 4).total <= static_cast<uint32_t>(max_smem);
 }
 
-template <uint32_t kRingSlots>
+template <uint32_t M_PAD, uint32_t kRingSlots>
 inline int launch_stacked_k_ring_instance(const GemmParams& p, const CUtensorMap& map_w, const CUtensorMap& map_x,
                                           uint32_t steps, uint32_t grid, cudaStream_t stream, bool programmatic) {
-    auto kernel = fp8_gemm_stacked_k_ring_kernel<kRingSlots>;
-    const uint32_t smem_ring = stacked_k_ring_smem_layout(steps, kRingSlots).total;
+    auto kernel = fp8_gemm_stacked_k_ring_kernel<M_PAD, kRingSlots>;
+    const uint32_t smem_ring = stacked_k_ring_smem_layout(M_PAD, steps, kRingSlots).total;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_ring) != cudaSuccess) {
         cudaGetLastError();
         return kSmemTooLarge;
@@ -449,8 +450,14 @@ inline bool stacked_k_supported(uint32_t m, uint32_t n, uint32_t k, int max_smem
 // True where the stacked form is the faster of the two weight-streaming kernels: M <= 16 and two CTAs resident per SM
 // (measured at N = 7168, K = 2048 with programmatic launch: 5.4 us against 6.3 us at M = 16; at M = 32 its CTAs
 // need 128 KB each, only one fits per SM, and the pair kernel wins, 7.2 us against 7.9 us).
-inline bool stacked_k_preferred(uint32_t m, uint32_t n, uint32_t k, int max_smem_per_block, int max_smem_per_sm) {
-    if (stacked_k_ring_supported(m, n, k, max_smem_per_block)) return true;  // 96 KB + scales: always two per SM
+inline bool stacked_k_preferred(uint32_t m, uint32_t n, uint32_t k, int max_smem_per_block, int max_smem_per_sm,
+                                int num_sms) {
+    // Long K: the ring variant against the general kernel, the only alternative there.  M <= 16: 96 KB + scales, two
+    // CTAs per SM, always faster (M=16, N=7168, K=4096: 9.7 vs 16.3 us).  M <= 32: 128 KB + scales, one CTA per SM:
+    // faster while the grid fits the GPU in one wave (N=4096, K=7168: 12.9 vs 15.8 us), slower beyond
+    // (N=7168, K=4096: 15.2 vs 11.6 us).
+    if (stacked_k_ring_supported(m, n, k, max_smem_per_block))
+        return m <= 16 || n / kStackedRows <= static_cast<uint32_t>(num_sms);
     if (m > 16 || !stacked_k_supported(m, n, k, max_smem_per_block)) return false;
     const uint32_t per_cta = stacked_k_smem_layout(16, k / (kBlockK * kStackFactor)).total + 1024u;  // + driver reserve
     return 2 * per_cta <= static_cast<uint32_t>(max_smem_per_sm);
@@ -520,10 +527,12 @@ inline int launch_fp8_gemm_stacked_k(const GemmArgs& a, cudaStream_t stream, boo
     if (ring) {
         int sm_count = 0;
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+        if (m_pad == 32)  // four slots of 128 accumulator columns are all of tensor memory
+            return launch_stacked_k_ring_instance<32, 4>(p, map_w, map_x, steps, grid, stream, programmatic);
         const bool alone_on_sm = grid <= static_cast<uint32_t>(sm_count) && steps > 4 &&
-                                 stacked_k_ring_smem_layout(steps, 8).total <= static_cast<uint32_t>(max_smem);
-        if (alone_on_sm) return launch_stacked_k_ring_instance<8>(p, map_w, map_x, steps, grid, stream, programmatic);
-        return launch_stacked_k_ring_instance<4>(p, map_w, map_x, steps, grid, stream, programmatic);
+                                 stacked_k_ring_smem_layout(16, steps, 8).total <= static_cast<uint32_t>(max_smem);
+        if (alone_on_sm) return launch_stacked_k_ring_instance<16, 8>(p, map_w, map_x, steps, grid, stream, programmatic);
+        return launch_stacked_k_ring_instance<16, 4>(p, map_w, map_x, steps, grid, stream, programmatic);
     }
     const uint32_t smem_bytes = stacked_k_smem_layout(m_pad, steps).total;
     if (m_pad == 16) return launch_stacked_k_instance<16>(p, map_w, map_x, smem_bytes, grid, stream, programmatic);
