@@ -221,6 +221,16 @@ void yan_b200_allreduce_bf16_in_switch(void* multicast, void* const* signals, in
  */
 void yan_b200_set_programmatic_dependent_launch(int enabled);
 
+/*
+ * Clock probe.  `device_buffer` = 16 int64 in device memory of the current device, or NULL to switch the probe off
+ * (default).  While set, CTA 0 of every general-kernel GEMM launch writes {clock64, globaltimer ns} when it starts
+ * ([0], [1]) and when it ends ([2], [3]); ([2]-[0]) / ([3]-[1]) is the SM clock in GHz the kernel really ran at, which
+ * a millisecond-period NVML sample cannot show for a kernel of a millisecond or two.  A library built with
+ * -DYAN_PHASE_STAMPS also fills [4..13] with per-role wait / work cycles of CTA 0 (slot list: include/gemm/fp8_gemm.cuh).
+ * Follows the reference's in-kernel clock64 stamps (yan/include/flash_attn/flash_attn_tk.cuh:56-63,159-164).
+ */
+void yan_b200_set_clock_probe(void* device_buffer);
+
 /* Sets the bound (nanoseconds, default 2e9) of every device-side wait of later GEMM launches. */
 void yan_b200_set_wait_timeout_ns(unsigned long long timeout_ns);
 

@@ -21,6 +21,7 @@ __device__ int g_status_word = 0;
 
 unsigned long long g_timeout_ns = 2000000000ull;
 int g_programmatic_launch = 0;
+long long* g_clock_probe = nullptr;
 
 constexpr int kMaxDevices = 64;
 int* g_status_ptr[kMaxDevices] = {};
@@ -116,6 +117,7 @@ int dispatch_gemm(yan::GemmType type, yan::OutKind out_kind, yan::GemmArgs& a, i
     }
     a.status = status_word_of_current_device();
     a.timeout_ns = g_timeout_ns;
+    a.clock_probe = g_clock_probe;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // M <= 64: the weight-streaming kernels.  block_n 1 asks for the pair-cluster kernel, 2 for the stacked-K kernel
     // (M <= 32), 0 picks the stacked one where it is the faster (M <= 16, two CTAs per SM), else the pair kernel.
@@ -471,6 +473,8 @@ YAN_EXPORT void yan_b200_allreduce_bf16_in_switch(void* multicast, void* const* 
 }
 
 YAN_EXPORT void yan_b200_set_programmatic_dependent_launch(int enabled) { g_programmatic_launch = enabled; }
+
+YAN_EXPORT void yan_b200_set_clock_probe(void* device_buffer) { g_clock_probe = static_cast<long long*>(device_buffer); }
 
 YAN_EXPORT void yan_b200_set_wait_timeout_ns(unsigned long long timeout_ns) {
     g_timeout_ns = timeout_ns == 0 ? 1 : timeout_ns;

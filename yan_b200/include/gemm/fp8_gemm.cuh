@@ -50,6 +50,9 @@ struct GemmParams {
     uint32_t num_groups;
     int* status;  // optional device word: 0 = fine, otherwise (kDeviceTimeout << 8) | site
     unsigned long long timeout_ns;
+    // optional: CTA 0 writes {clock64, globaltimer} when it starts and when it ends (4 values), so that the host can
+    // derive the SM clock the kernel really ran at (cycles / nanoseconds), which a millisecond-period NVML sample misses
+    long long* clock_probe = nullptr;
 };
 
 namespace detail {
@@ -65,6 +68,9 @@ __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, vol
     const uint64_t t0 = ptx::globaltimer_ns();
     uint32_t spins = 0;
     while (!ptx::mbar_try_wait(bar, parity)) {
+#if defined(YAN_PRODUCER_POLL_SLEEP_NS) && YAN_PRODUCER_POLL_SLEEP_NS > 0
+        if (site == 1) __nanosleep(YAN_PRODUCER_POLL_SLEEP_NS);  // the TMA producer runs stages ahead: it can poll lazily
+#endif
         if ((++spins & 0x3Fu) == 0) {
             if (*abort_flag != 0) return false;
             if (ptx::globaltimer_ns() - t0 > p.timeout_ns) {
@@ -153,8 +159,17 @@ struct GemmSmemLayout {
     static constexpr uint32_t SMEM_B_SIZE_PER_STAGE = BLOCK_N * kBlockK;
     static constexpr uint32_t kOffA = 0;
     static constexpr uint32_t kOffB = kOffA + kNumStages * SMEM_A_SIZE_PER_STAGE;
-    static constexpr uint32_t kOffBarriers = kOffB + kNumStages * SMEM_B_SIZE_PER_STAGE;
-    static constexpr uint32_t kNumBarriers = 2 * kNumStages + 2 * kNumTmemBufs;
+    // Output staging: every promotion warp owns one 32-row x 128-byte box (4 KB, 1024-byte aligned) that it fills with
+    // 16-byte shared-memory stores and hands to a TMA store, so that the output leaves the SM as whole 128-byte lines.
+    // Only the widths whose ring leaves room for it have one (the others store from registers).
+    static constexpr uint32_t kStoreBoxBytes = 4096;
+    static constexpr uint32_t kNumStoreBoxes = 8;
+    static constexpr uint32_t kOffStore = kOffB + kNumStages * SMEM_B_SIZE_PER_STAGE;
+    static constexpr uint32_t kStoreBytes =
+        (kOffStore + kNumStoreBoxes * kStoreBoxBytes + 2048 <= 232448 && kOffStore % 1024 == 0) ? kNumStoreBoxes * kStoreBoxBytes : 0;
+    static constexpr uint32_t kOffBarriers = kOffStore + kStoreBytes;
+    // ring full/empty, TMEM full/empty per buffer and column half
+    static constexpr uint32_t kNumBarriers = 2 * kNumStages + 4 * kNumTmemBufs;
     static constexpr uint32_t kOffTmemSlot = kOffBarriers + kNumBarriers * 8;
     static constexpr uint32_t kOffAbort = kOffTmemSlot + 4;
     // +1024: the dynamic shared-memory base is re-aligned to 1024 bytes inside the kernel.
@@ -163,22 +178,64 @@ struct GemmSmemLayout {
     static_assert(BLOCK_N % 32 == 0 && BLOCK_N >= 32 && BLOCK_N <= 256, "UMMA M=128 needs N % 16 == 0, N <= 256");
 };
 
+// Compile-time knobs of the promotion (defaults = the measured best on B200; the others stay selectable for the tuner
+// and for measurements):
+//   YAN_PROMO_CHUNK        columns per tcgen05.ld (8, 16 or 32).
+//   YAN_PROMO_SPLIT_HALVES 1: the MMA thread issues each k-block as two half-width MMA streams (columns [0, N/2) then
+//                          [N/2, N)), each with its own TMEM-full / TMEM-empty barrier: warpgroup 0 is released half a
+//                          k-block before warpgroup 1 (so the two warps that share an SM sub-partition do not load and
+//                          multiply in lockstep) and each half of a TMEM buffer is recycled as soon as its own
+//                          warpgroup has read it.  0: one full-width stream, one barrier pair per buffer.
+//   YAN_PROMO_EARLY_PROBE  1: the next k-block's TMEM-full barrier is probed (without blocking) right after this
+//                          k-block's last load, so that the answer arrives under the last FMAs.
+// Measured and dropped: handing the TMEM read port back and forth between the two warps of a sub-partition through
+// mbarriers (an arrive-to-wait hand-over costs ~100 cycles: 778 and 1163 cycles per k-block for 64- and 32-column turns
+// against 343 without), and four promotion warpgroups (874 cycles per k-block against 733: the per-k-block bookkeeping
+// of sixteen warps fills the issue slots).
+#ifndef YAN_PROMO_CHUNK
+#define YAN_PROMO_CHUNK 16
+#endif
+#ifndef YAN_PROMO_SPLIT_HALVES
+#define YAN_PROMO_SPLIT_HALVES 0
+#endif
+#ifndef YAN_PROMO_EARLY_PROBE
+#define YAN_PROMO_EARLY_PROBE 0
+#endif
+
+// -DYAN_PHASE_STAMPS: CTA 0 also accumulates, per role, the cycles it spends waiting and working and writes them
+// behind the four clock values of GemmParams::clock_probe (the per-SM clock64 stamps of the reference's
+// yan/include/flash_attn/flash_attn_tk.cuh:56-63,159-164).  Slots: [4] producer waiting for a free stage,
+// [5] MMA thread waiting for operands, [6] MMA thread waiting for a free TMEM buffer, [7] MMA thread total,
+// [8] promotion warp 4 waiting for a full TMEM buffer, [9] its TMEM loads, [10] its FMAs (issue time),
+// [11] its total, [12] k-blocks it promoted, [13] its epilogue stores.  The clock reads perturb the schedule
+// a little: use the flag to see where time goes, not to time the kernel.
+#ifdef YAN_PHASE_STAMPS
+#define YAN_STAMP(var) const long long var = clock64()
+#define YAN_STAMP_ADD(acc, from, to) acc += (to) - (from)
+#else
+#define YAN_STAMP(var)
+#define YAN_STAMP_ADD(acc, from, to)
+#endif
+
 template <uint32_t BLOCK_N, uint32_t kNumStages, GemmType kGemmType, typename out_t>
 __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     fp8_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tensor_map_a,
-                    const __grid_constant__ CUtensorMap tensor_map_b) {
+                    const __grid_constant__ CUtensorMap tensor_map_b, const __grid_constant__ CUtensorMap tensor_map_d) {
 #if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ >= 1000)
     using L = GemmSmemLayout<BLOCK_N, kNumStages>;
     using Sched = Scheduler<kGemmType, kBlockM, BLOCK_N>;
     constexpr uint32_t kNumTmemBufs = L::kNumTmemBufs;
     constexpr uint32_t kNumMathWGs = get_num_math_warpgroups(BLOCK_N);
+    static_assert(kNumMathWGs == 2 || YAN_PROMO_SPLIT_HALVES == 0, "the half-width streams assume two promotion warpgroups");
     static_assert(RegisterBudgetCheck<BLOCK_N>::ok);
     constexpr uint32_t kColsPerWG = BLOCK_N / kNumMathWGs;
     constexpr uint32_t kNumMathWarps = 4 * kNumMathWGs;
     // Columns move TMEM -> registers in chunks of 32 (the fastest tcgen05.ld shape measured) plus, when BLOCK_N/2 is
     // not a multiple of 32 (BLOCK_N = 224, 160, 96), one chunk of 16.
     static_assert(kColsPerWG % 16 == 0, "a promotion warpgroup owns a multiple of 16 columns");
-    constexpr uint32_t kChunk = kColsPerWG < 32 ? kColsPerWG : 32;
+    static_assert(YAN_PROMO_CHUNK == 8 || YAN_PROMO_CHUNK == 16 || YAN_PROMO_CHUNK == 32);
+    constexpr uint32_t kChunk = kColsPerWG < YAN_PROMO_CHUNK ? kColsPerWG : YAN_PROMO_CHUNK;
+    constexpr bool kEarlyProbe = (YAN_PROMO_EARLY_PROBE != 0);
     constexpr uint32_t kNumChunks = kColsPerWG / kChunk;
     constexpr uint32_t kTailChunk = kColsPerWG - kNumChunks * kChunk;  // 0 or 16
     static_assert(kTailChunk == 0 || kTailChunk == 16);
@@ -187,15 +244,26 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     // multiple of 16 columns: two B scales per k-block, chosen per group of 16 columns (the case the reference
     // handles for BLOCK_N not dividing BLOCK_K, fp8_gemm.cuh:55-61,149-160).
     constexpr bool kTwoScales = (128 % kColsPerWG != 0) && (kColsPerWG % 128 != 0);
-    constexpr uint32_t kScaleDepth = 4;
+#ifndef YAN_PROMO_SCALE_DEPTH
+#define YAN_PROMO_SCALE_DEPTH 4
+#endif
+    constexpr uint32_t kScaleDepth = YAN_PROMO_SCALE_DEPTH;
+    // bf16 / fp32 output through the staging boxes and TMA stores (see GemmSmemLayout).  The masked grouped kind keeps
+    // register stores: its row limit is per group, which a tensor map cannot clip.
+    constexpr bool kStagedStore = L::kStoreBytes != 0 && sizeof(out_t) >= 2 && kGemmType != GemmType::GroupedMasked &&
+                                  kNumMathWarps == L::kNumStoreBoxes && (kColsPerWG * sizeof(out_t)) % 128 == 0;
+    constexpr uint32_t kStoreCols = 128 / (sizeof(out_t) >= 2 ? sizeof(out_t) : 2);  // columns per 128-byte box row
+    // Half-width MMA streams: each warpgroup's columns are produced and recycled on their own barriers.
+    constexpr bool kSplitHalves = (YAN_PROMO_SPLIT_HALVES != 0);
+    constexpr uint32_t kNumHalves = kSplitHalves ? 2 : 1;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
 
     uint64_t* full_barriers = reinterpret_cast<uint64_t*>(smem + L::kOffBarriers);
     uint64_t* empty_barriers = full_barriers + kNumStages;
-    uint64_t* tmem_full_barriers = empty_barriers + kNumStages;
-    uint64_t* tmem_empty_barriers = tmem_full_barriers + kNumTmemBufs;
+    uint64_t* tmem_full_barriers = empty_barriers + kNumStages;            // [buf][half]
+    uint64_t* tmem_empty_barriers = tmem_full_barriers + 2 * kNumTmemBufs;  // [buf][half]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kOffTmemSlot);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kOffAbort);
 
@@ -207,6 +275,7 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     if (warp_idx == 0 && lane_idx == 0) {
         ptx::tma_prefetch_desc(&tensor_map_a);
         ptx::tma_prefetch_desc(&tensor_map_b);
+        if constexpr (kStagedStore) ptx::tma_prefetch_desc(&tensor_map_d);
     }
     if (warp_idx == 1 && lane_idx == 0) {
 #pragma unroll
@@ -215,9 +284,9 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
             ptx::mbar_init(empty_barriers + i, 1);  // tcgen05.commit of the MMA thread
         }
 #pragma unroll
-        for (uint32_t i = 0; i < kNumTmemBufs; ++i) {
-            ptx::mbar_init(tmem_full_barriers + i, 1);               // tcgen05.commit
-            ptx::mbar_init(tmem_empty_barriers + i, kNumMathWarps);  // one arrival per promotion warp
+        for (uint32_t i = 0; i < 2 * kNumTmemBufs; ++i) {
+            ptx::mbar_init(tmem_full_barriers + i, 1);                             // tcgen05.commit
+            ptx::mbar_init(tmem_empty_barriers + i, kNumMathWarps / kNumHalves);  // one arrival per promotion warp
         }
         *abort_flag = 0;
         ptx::fence_barrier_init();
@@ -231,6 +300,10 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     __syncthreads();
     ptx::tcgen05_fence_after_thread_sync();
     const uint32_t tmem_base = *tmem_slot;
+    if (p.clock_probe != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+        p.clock_probe[0] = clock64();
+        p.clock_probe[1] = static_cast<long long>(ptx::globaltimer_ns());
+    }
 
     if (warp_idx < 4) {
         ptx::reg_dealloc<get_num_control_registers(BLOCK_N)>();
@@ -240,16 +313,20 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
             Sched sched(p.shape_m, p.shape_n, p.grouped_layout, p.num_groups);
             uint32_t m_block_idx, n_block_idx, stage = 0, phase = 0;
             bool alive = true;
+            [[maybe_unused]] long long waited_empty = 0;
             while (alive && sched.get_next_block(m_block_idx, n_block_idx)) {
                 const int group = sched.get_group(m_block_idx);
                 if (group < 0) continue;
                 const int32_t a_row = static_cast<int32_t>(sched.get_row_base(m_block_idx));
                 const int32_t b_row = static_cast<int32_t>(group * p.shape_n + n_block_idx * BLOCK_N);
                 for (uint32_t kb = 0; kb < num_k_blocks; ++kb) {
+                    YAN_STAMP(w0);
                     if (!detail::bounded_wait(empty_barriers + stage, phase ^ 1, abort_flag, p, 1)) {
                         alive = false;
                         break;
                     }
+                    YAN_STAMP(w1);
+                    YAN_STAMP_ADD(waited_empty, w0, w1);
                     ptx::mbar_arrive_expect_tx(full_barriers + stage,
                                                L::SMEM_A_SIZE_PER_STAGE + L::SMEM_B_SIZE_PER_STAGE);
                     ptx::tma_load_2d(smem + L::kOffA + stage * L::SMEM_A_SIZE_PER_STAGE, &tensor_map_a,
@@ -262,6 +339,9 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
                     }
                 }
             }
+#ifdef YAN_PHASE_STAMPS
+            if (p.clock_probe != nullptr && blockIdx.x == 0) p.clock_probe[4] = waited_empty;
+#endif
             if (!alive) {
                 // Give copies still in flight time to land before the CTA's shared memory is released.
                 const uint64_t t0 = ptx::globaltimer_ns();
@@ -270,28 +350,48 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
         } else if (warp_idx == 1 && lane_idx == 0) {
             // ------------------------------ MMA issuer ------------------------------
             Sched sched(p.shape_m, p.shape_n, p.grouped_layout, p.num_groups);
-            constexpr uint32_t idesc = make_instr_desc_e4m3_f32(kBlockM, BLOCK_N);
+            constexpr uint32_t kUmmaN = BLOCK_N / kNumHalves;
+            constexpr uint32_t idesc = make_instr_desc_e4m3_f32(kBlockM, kUmmaN);
+            // rows [kUmmaN, BLOCK_N) of the B tile start kUmmaN 128-byte rows further on (whole 8-row swizzle atoms)
+            constexpr uint32_t kDescHalfStep = (kUmmaN * kBlockK) >> 4;
+            static_assert(kUmmaN % 16 == 0, "UMMA with M = 128 needs N % 16 == 0");
             uint32_t m_block_idx, n_block_idx, stage = 0, phase = 0, buf = 0, buf_phase = 0;
             bool alive = true;
+            [[maybe_unused]] long long waited_full = 0, waited_tmem = 0;
+            YAN_STAMP(mma_begin);
             while (alive && sched.get_next_block(m_block_idx, n_block_idx)) {
                 if (sched.get_group(m_block_idx) < 0) continue;
-                for (uint32_t kb = 0; kb < num_k_blocks; ++kb) {
-                    if (!detail::bounded_wait(full_barriers + stage, phase, abort_flag, p, 2) ||
-                        !detail::bounded_wait(tmem_empty_barriers + buf, buf_phase ^ 1, abort_flag, p, 3)) {
+                for (uint32_t kb = 0; kb < num_k_blocks && alive; ++kb) {
+                    YAN_STAMP(w0);
+                    if (!detail::bounded_wait(full_barriers + stage, phase, abort_flag, p, 2)) {
                         alive = false;
                         break;
                     }
-                    ptx::tcgen05_fence_after_thread_sync();
+                    YAN_STAMP(w1);
+                    YAN_STAMP_ADD(waited_full, w0, w1);
                     const uint64_t a_desc =
                         make_smem_desc_k_major_sw128(ptx::smem_u32(smem + L::kOffA + stage * L::SMEM_A_SIZE_PER_STAGE));
                     const uint64_t b_desc =
                         make_smem_desc_k_major_sw128(ptx::smem_u32(smem + L::kOffB + stage * L::SMEM_B_SIZE_PER_STAGE));
-                    const uint32_t tmem_d = tmem_base + buf * BLOCK_N;
 #pragma unroll
-                    for (uint32_t k = 0; k < kBlockK / kUmmaK; ++k)
-                        ptx::umma_f8f6f4_ss(tmem_d, a_desc + k * kDescKStep, b_desc + k * kDescKStep, idesc, k > 0);
-                    ptx::umma_commit(empty_barriers + stage);      // smem stage reusable once these MMAs are done
-                    ptx::umma_commit(tmem_full_barriers + buf);    // partial sum of this k-block is complete
+                    for (uint32_t h = 0; h < kNumHalves; ++h) {
+                        YAN_STAMP(w2);
+                        if (!detail::bounded_wait(tmem_empty_barriers + buf * 2 + h, buf_phase ^ 1, abort_flag, p, 3)) {
+                            alive = false;
+                            break;
+                        }
+                        YAN_STAMP(w3);
+                        YAN_STAMP_ADD(waited_tmem, w2, w3);
+                        ptx::tcgen05_fence_after_thread_sync();
+                        const uint32_t tmem_d = tmem_base + buf * BLOCK_N + h * kUmmaN;
+#pragma unroll
+                        for (uint32_t k = 0; k < kBlockK / kUmmaK; ++k)
+                            ptx::umma_f8f6f4_ss(tmem_d, a_desc + k * kDescKStep, b_desc + h * kDescHalfStep + k * kDescKStep,
+                                                idesc, k > 0);
+                        if (h + 1 == kNumHalves)
+                            ptx::umma_commit(empty_barriers + stage);       // smem stage reusable once these MMAs are done
+                        ptx::umma_commit(tmem_full_barriers + buf * 2 + h);  // partial sum of this k-block is complete
+                    }
                     if (++stage == kNumStages) {
                         stage = 0;
                         phase ^= 1;
@@ -302,6 +402,13 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
                     }
                 }
             }
+#ifdef YAN_PHASE_STAMPS
+            if (p.clock_probe != nullptr && blockIdx.x == 0) {
+                p.clock_probe[5] = waited_full;
+                p.clock_probe[6] = waited_tmem;
+                p.clock_probe[7] = clock64() - mma_begin;
+            }
+#endif
         }
         __syncwarp();
     } else {
@@ -313,11 +420,14 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
         const uint32_t row_in_tile = quarter * 32 + lane_idx;
         const uint32_t col0 = wg * kColsPerWG;
         const uint32_t tmem_lane_base = tmem_base + ((quarter * 32u) << 16) + col0;
+        const uint32_t half = kSplitHalves ? wg : 0;
 
         Sched sched(p.shape_m, p.shape_n, p.grouped_layout, p.num_groups);
         uint32_t m_block_idx, n_block_idx, buf = 0, buf_phase = 0;
-        bool alive = true;
+        bool alive = true, next_ready = false;
         float acc[kColsPerWG];
+        [[maybe_unused]] long long waited_tmem_full = 0, in_loads = 0, in_fmas = 0, in_stores = 0, promoted = 0;
+        YAN_STAMP(promo_begin);
 
         while (alive && sched.get_next_block(m_block_idx, n_block_idx)) {
             const int group = sched.get_group(m_block_idx);
@@ -328,6 +438,7 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
             const uint32_t sb_row = min(n_first / 128u, num_sb_rows - 1);
             const float* sa_ptr = p.scales_a + row;
             const float* sb_ptr = p.scales_b + (static_cast<size_t>(group) * num_sb_rows + sb_row) * num_k_blocks;
+            const float* sa_next = sa_ptr + static_cast<size_t>(kScaleDepth) * p.sa_ld;  // row's scale kScaleDepth k-blocks ahead
             // two-scale case: groups of 16 columns from `hi_from` on belong to the next 128-column block
             const uint32_t hi_from = kTwoScales ? (128u - n_first % 128u) / 16u : 0xFFFFu;
             const float* sb_hi_ptr =
@@ -353,43 +464,57 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
                     float scale_hi = scale;
                     if constexpr (kTwoScales) scale_hi = sa_ring[i] * sb_hi_ring[i];
                     if (kb + kScaleDepth < num_k_blocks) {
-                        sa_ring[i] = row_ok ? __ldg(sa_ptr + static_cast<size_t>(kb + kScaleDepth) * p.sa_ld) : 0.0f;
+                        sa_ring[i] = row_ok ? __ldg(sa_next) : 0.0f;
+                        sa_next += p.sa_ld;
                         sb_ring[i] = __ldg(sb_ptr + kb + kScaleDepth);
                         if constexpr (kTwoScales) sb_hi_ring[i] = __ldg(sb_hi_ptr + kb + kScaleDepth);
                     }
-                    const bool ok = detail::bounded_wait(tmem_full_barriers + buf, buf_phase, abort_flag, p, 4);
+                    YAN_STAMP(w0);
+                    const bool ok = (kEarlyProbe && next_ready) ||
+                                    detail::bounded_wait(tmem_full_barriers + buf * 2 + half, buf_phase, abort_flag, p, 4);
                     if (!__all_sync(0xffffffffu, ok)) {
                         alive = false;
                         continue;
                     }
+                    YAN_STAMP(w1);
+                    YAN_STAMP_ADD(waited_tmem_full, w0, w1);
+                    YAN_STAMP_ADD(promoted, 0, 1);
                     ptx::tcgen05_fence_after_thread_sync();
                     const uint32_t taddr = tmem_lane_base + buf * BLOCK_N;
 
-                    // The TMEM buffer is handed back as soon as the last chunk has landed, before its FMAs.
+                    // The TMEM buffer is handed back as soon as the last columns have landed, before their FMAs.
                     // Nothing is scheduled between a tcgen05.ld and its wait: FMAs issued while a load is
                     // outstanding were measured ~10x slower than after it (the load does not overlap with the
-                    // issuing warp's own arithmetic), so a second landing buffer buys nothing.  Also measured and
-                    // slower: postponing warpgroup 1's last chunk to its next k-block so that the two warps of
-                    // a sub-partition alternate between loading and multiplying (1.93 vs 2.17 PFLOP/s on C4).
+                    // issuing warp's own arithmetic), so the overlap has to come from the sibling warp.
                     auto release_buffer = [&]() {
                         ptx::tcgen05_fence_before_thread_sync();
                         __syncwarp();
-                        if (lane_idx == 0) ptx::mbar_arrive(tmem_empty_barriers + buf);
+                        if (lane_idx == 0) ptx::mbar_arrive(tmem_empty_barriers + buf * 2 + half);
                     };
                     auto group_scale = [&](uint32_t group16) { return (kTwoScales && group16 >= hi_from) ? scale_hi : scale; };
 #pragma unroll
                     for (uint32_t c = 0; c < kNumChunks; ++c) {
                         uint32_t t[kChunk];
+                        YAN_STAMP(l0);
                         ptx::tmem_ld_32x32b<kChunk>(taddr + c * kChunk, t);
                         ptx::tmem_ld_wait<kChunk>(t);
-                        if (kTailChunk == 0 && c + 1 == kNumChunks) release_buffer();
-#pragma unroll
-                        for (uint32_t h = 0; h < kChunk / 16; ++h) {
-                            const float sc = group_scale((c * kChunk) / 16 + h);
-#pragma unroll
-                            for (uint32_t j = h * 16; j < h * 16 + 16; ++j)
-                                acc[c * kChunk + j] = fmaf(sc, __uint_as_float(t[j]), acc[c * kChunk + j]);
+                        YAN_STAMP(l1);
+                        YAN_STAMP_ADD(in_loads, l0, l1);
+                        if (kTailChunk == 0 && c + 1 == kNumChunks) {
+                            release_buffer();
+                            if constexpr (kEarlyProbe) {
+                                const uint32_t nb = (buf + 1 == kNumTmemBufs) ? 0 : buf + 1;
+                                const uint32_t np = (buf + 1 == kNumTmemBufs) ? buf_phase ^ 1 : buf_phase;
+                                next_ready = __all_sync(0xffffffffu, ptx::mbar_test_wait(tmem_full_barriers + nb * 2 + half, np));
+                            }
                         }
+#pragma unroll
+                        for (uint32_t j = 0; j < kChunk; ++j) {
+                            const float sc = group_scale((c * kChunk + j) / 16);
+                            acc[c * kChunk + j] = fmaf(sc, __uint_as_float(t[j]), acc[c * kChunk + j]);
+                        }
+                        YAN_STAMP(l2);
+                        YAN_STAMP_ADD(in_fmas, l1, l2);
                     }
                     if constexpr (kTailChunk != 0) {
                         uint32_t t[16];
@@ -407,18 +532,74 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
                     }
                 }
             }
+            YAN_STAMP(s0);
             if (alive && row_ok) {
-                if constexpr (sizeof(out_t) == 1) {
-                    static_assert(kColsPerWG == 128, "the e4m3 output needs one 128-column group per thread: BLOCK_N = 256");
+                if constexpr (sizeof(out_t) == 1 && kColsPerWG != 128) {
+                    // the e4m3 output needs one 128-column group per thread (BLOCK_N = 256, two warpgroups): the launcher
+                    // refuses every other shape of CTA
+                } else if constexpr (sizeof(out_t) == 1) {
                     if (n_first < p.shape_n)
                         detail::store_row_e4m3(
                             reinterpret_cast<uint8_t*>(p.out) + static_cast<size_t>(row) * p.ldd + n_first,
                             p.out_scales + static_cast<size_t>(n_first / 128u) * p.out_scales_ld + row, acc);
-                } else {
+                } else if constexpr (!kStagedStore) {
                     out_t* dst = reinterpret_cast<out_t*>(p.out) + static_cast<size_t>(row) * p.ldd + n_first;
                     detail::store_row<out_t, kColsPerWG>(dst, acc, n_first, p.shape_n);
                 }
             }
+            if constexpr (kStagedStore) {
+                if (alive) {
+                    // Lane r fills row r of the warp's box; 16-byte chunk j of a row sits at chunk j ^ (r % 8), the
+                    // 128-byte swizzle the tensor map expects.  Rows past the matrix hold zeros and are clipped by the store.
+                    uint8_t* box = smem + L::kOffStore + (warp_idx - 4) * L::kStoreBoxBytes;
+                    const uint32_t row_addr = ptx::smem_u32(box) + lane_idx * 128u;
+#pragma unroll
+                    for (uint32_t pass = 0; pass < kColsPerWG / kStoreCols; ++pass) {
+                        if (lane_idx == 0) ptx::tma_store_wait_read<0>();  // the previous store has read the box
+                        __syncwarp();
+#pragma unroll
+                        for (uint32_t j = 0; j < 8; ++j) {
+                            const float* a = acc + pass * kStoreCols + j * (16 / sizeof(out_t));
+                            uint4 v;
+                            if constexpr (sizeof(out_t) == 2) {
+                                __nv_bfloat162 t0 = __floats2bfloat162_rn(a[0], a[1]), t1 = __floats2bfloat162_rn(a[2], a[3]);
+                                __nv_bfloat162 t2 = __floats2bfloat162_rn(a[4], a[5]), t3 = __floats2bfloat162_rn(a[6], a[7]);
+                                v.x = *reinterpret_cast<uint32_t*>(&t0);
+                                v.y = *reinterpret_cast<uint32_t*>(&t1);
+                                v.z = *reinterpret_cast<uint32_t*>(&t2);
+                                v.w = *reinterpret_cast<uint32_t*>(&t3);
+                            } else {
+                                v = make_uint4(__float_as_uint(a[0]), __float_as_uint(a[1]), __float_as_uint(a[2]),
+                                               __float_as_uint(a[3]));
+                            }
+                            ptx::st_shared_v4(row_addr + ((j ^ (lane_idx & 7u)) << 4), v);
+                        }
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                        const uint32_t n_pass = n_first + pass * kStoreCols;
+                        if (lane_idx == 0 && n_pass < p.shape_n) {
+                            ptx::tma_store_2d(&tensor_map_d, box, static_cast<int32_t>(n_pass),
+                                              static_cast<int32_t>(sched.get_row_base(m_block_idx) + quarter * 32u));
+                            ptx::tma_store_commit();
+                        }
+                    }
+                }
+            }
+            YAN_STAMP(s1);
+            YAN_STAMP_ADD(in_stores, s0, s1);
+        }
+#ifdef YAN_PHASE_STAMPS
+        if (p.clock_probe != nullptr && blockIdx.x == 0 && warp_idx == 4 && lane_idx == 0) {
+            p.clock_probe[8] = waited_tmem_full;
+            p.clock_probe[9] = in_loads;
+            p.clock_probe[10] = in_fmas;
+            p.clock_probe[11] = clock64() - promo_begin;
+            p.clock_probe[12] = promoted;
+            p.clock_probe[13] = in_stores;
+        }
+#endif
+        if constexpr (kStagedStore) {
+            if (lane_idx == 0) ptx::tma_store_wait<0>();  // the boxes stay valid until the last store has completed
         }
         __syncwarp();
     }
@@ -429,6 +610,10 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     if (warp_idx == 2) {
         ptx::tcgen05_fence_after_thread_sync();
         ptx::tmem_dealloc(tmem_base, L::kTmemCols);
+    }
+    if (p.clock_probe != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+        p.clock_probe[2] = clock64();
+        p.clock_probe[3] = static_cast<long long>(ptx::globaltimer_ns());
     }
 #endif
 }
@@ -451,6 +636,7 @@ struct GemmArgs {
     int num_sms = 0;
     int* status = nullptr;
     unsigned long long timeout_ns = 2000000000ull;
+    long long* clock_probe = nullptr;  // optional: 4 values written by CTA 0 (see GemmParams)
 };
 
 inline bool is_aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
@@ -495,6 +681,9 @@ struct GemmLauncher {
         bool ok = true;
         const CUtensorMap map_a = make_2d_tma_desc_u8_sw128(a.lhs, a_rows, a.k, a.k, kBlockM, ok);
         const CUtensorMap map_b = make_2d_tma_desc_u8_sw128(a.rhs, b_rows, a.k, a.k, BLOCK_N, ok);
+        CUtensorMap map_d{};  // only the kinds that stage their output read it
+        if (L::kStoreBytes != 0 && sizeof(out_t) >= 2 && kGemmType != GemmType::GroupedMasked)
+            map_d = make_2d_tma_store_desc_sw128(a.out, a_rows, a.n, a.ldd, sizeof(out_t), ok);
         if (!ok) return kTensorMapFailed;
 
         GemmParams p;
@@ -512,6 +701,7 @@ struct GemmLauncher {
         p.num_groups = a.num_groups;
         p.status = a.status;
         p.timeout_ns = a.timeout_ns;
+        p.clock_probe = a.clock_probe;
 
         auto kernel = fp8_gemm_kernel<BLOCK_N, kNumStages, kGemmType, out_t>;
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemSize) != cudaSuccess) {
@@ -523,7 +713,7 @@ struct GemmLauncher {
             const uint32_t tiles = ceil_div(a.m, kBlockM) * ceil_div(a.n, BLOCK_N);
             grid = tiles < grid ? tiles : grid;
         }
-        kernel<<<grid, get_num_threads_per_sm<>(BLOCK_N), kSmemSize, stream>>>(p, map_a, map_b);
+        kernel<<<grid, get_num_threads_per_sm<>(BLOCK_N), kSmemSize, stream>>>(p, map_a, map_b, map_d);
         return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
     }
 };

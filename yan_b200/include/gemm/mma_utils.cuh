@@ -24,7 +24,12 @@ namespace yan {
 constexpr uint32_t kNumControlThreads = 128;
 constexpr uint32_t kNumMathThreadsPerGroup = 128;
 
-__host__ __device__ constexpr uint32_t get_num_math_warpgroups(uint32_t /*block_n*/) { return 2; }
+#ifndef YAN_NUM_MATH_WARPGROUPS
+#define YAN_NUM_MATH_WARPGROUPS 2
+#endif
+__host__ __device__ constexpr uint32_t get_num_math_warpgroups(uint32_t block_n) {
+    return (YAN_NUM_MATH_WARPGROUPS == 4 && block_n % 64 == 0) ? 4 : 2;
+}
 
 template <uint32_t kNumTMAThreads = kNumControlThreads, uint32_t kNumMathThreads = kNumMathThreadsPerGroup>
 __host__ __device__ constexpr uint32_t get_num_threads_per_sm(uint32_t block_n) {

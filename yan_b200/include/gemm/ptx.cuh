@@ -74,6 +74,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Non-blocking probe of a phase: returns at once (try_wait may park the thread for a while when the phase is open).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // ---------------------------------------------------------------------------------------------
 // TMA: 2D tiled load, global -> shared::cta of the issuing CTA, completion on an mbarrier.
 // No cluster multicast anywhere: every CTA fetches its own tiles.
@@ -97,6 +112,11 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* desc, const void
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
                      reinterpret_cast<uint64_t>(desc)),
                  "r"(smem_u32(smem_src)), "r"(c_inner), "r"(c_outer)
+                 : "memory");
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t smem_addr, const uint4& v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(smem_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                  : "memory");
 }
 
@@ -192,8 +212,26 @@ __device__ __forceinline__ void tmem_ld_32x32b<16>(uint32_t taddr, uint32_t (&r)
         : "memory");
 }
 
+template <>
+__device__ __forceinline__ void tmem_ld_32x32b<8>(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+        : "r"(taddr)
+        : "memory");
+}
+
 template <uint32_t N>
 __device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[N]);
+
+template <>
+__device__ __forceinline__ void tmem_ld_wait<8>(uint32_t (&r)[8]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])
+                 :
+                 : "memory");
+}
 
 template <>
 __device__ __forceinline__ void tmem_ld_wait<32>(uint32_t (&r)[32]) {

@@ -55,10 +55,13 @@ _DEFAULT_STAGES = {32: 8, 64: 8, 96: 8, 128: 6, 160: 6, 192: 5, 224: 5, 256: 4}
 
 
 def get_smem_size(block_n: int, num_stages: int) -> int:
-    """Dynamic shared memory of one CTA: stages x (A 128x128 + B BLOCK_Nx128 e4m3) + mbarriers +
-    1024 bytes of alignment slack (GemmSmemLayout in include/gemm/fp8_gemm.cuh)."""
+    """Dynamic shared memory of one CTA: stages x (A 128x128 + B BLOCK_Nx128 e4m3) + the output staging boxes
+    (8 x 4 KB, where the ring leaves room) + mbarriers + 1024 bytes of alignment slack (GemmSmemLayout in
+    include/gemm/fp8_gemm.cuh)."""
     num_tmem_bufs = 2 if block_n > 128 else 4
-    return num_stages * (128 * 128 + block_n * 128) + (2 * num_stages + 2 * num_tmem_bufs) * 8 + 8 + 1024
+    ring = num_stages * (128 * 128 + block_n * 128)
+    store = 8 * 4096 if (ring + 8 * 4096 + 2048 <= 232448 and ring % 1024 == 0) else 0
+    return ring + store + (2 * num_stages + 4 * num_tmem_bufs) * 8 + 8 + 1024
 
 
 # time of one tile relative to a 256-wide one (measured; see choose_block_n in csrc/capi.cu)
@@ -269,6 +272,23 @@ def set_programmatic_dependent_launch(enabled: bool) -> None:
     still running (programmatic dependent launch), and lets the quantizer inside fp8_linear be launched over the tail of
     the kernel before it.  Only valid when the weights are not produced by the kernel that precedes a GEMM."""
     _lib.lib().yan_b200_set_programmatic_dependent_launch(int(bool(enabled)))
+
+
+def set_clock_probe(buffer: Optional[torch.Tensor]) -> None:
+    """Points the kernels' clock probe at `buffer` (int64, >= 16 elements, on the current device) or switches it off
+    (None).  After a general-kernel GEMM, buffer[0:4] = CTA 0's {clock64, globaltimer ns} at start and end; see
+    `effective_sm_clock_mhz`.  (The reference stamps clock64 per SM the same way, flash_attn_tk.cuh:56-63.)"""
+    if buffer is None:
+        _lib.lib().yan_b200_set_clock_probe(None)
+        return
+    assert buffer.is_cuda and buffer.dtype == torch.int64 and buffer.numel() >= 16 and buffer.is_contiguous()
+    _lib.lib().yan_b200_set_clock_probe(buffer.data_ptr())
+
+
+def effective_sm_clock_mhz(buffer: torch.Tensor) -> float:
+    """SM clock the last probed GEMM ran at: CTA 0's clock64 delta over its globaltimer delta."""
+    v = buffer[:4].tolist()
+    return 1000.0 * (v[2] - v[0]) / max(v[3] - v[1], 1)
 
 
 def read_device_status(reset: bool = True) -> int:
