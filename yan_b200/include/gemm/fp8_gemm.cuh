@@ -159,14 +159,14 @@ struct GemmSmemLayout {
     static constexpr uint32_t SMEM_B_SIZE_PER_STAGE = BLOCK_N * kBlockK;
     static constexpr uint32_t kOffA = 0;
     static constexpr uint32_t kOffB = kOffA + kNumStages * SMEM_A_SIZE_PER_STAGE;
-    // Output staging: every promotion warp owns one 32-row x 128-byte box (4 KB, 1024-byte aligned) that it fills with
-    // 16-byte shared-memory stores and hands to a TMA store, so that the output leaves the SM as whole 128-byte lines.
-    // Only the widths whose ring leaves room for it have one (the others store from registers).
-    static constexpr uint32_t kStoreBoxBytes = 4096;
+    // Output staging: every promotion warp owns one 32-row x 64-byte box (2 KB).  A lane writes 64 bytes of its own
+    // output row into the box, the warp reads the box back eight rows at a time and stores 64 contiguous bytes per
+    // row piece, so that one store instruction covers 8 x 64 bytes instead of 32 x 16 bytes of 32 different lines.
+    static constexpr uint32_t kStoreBoxBytes = 2048;
     static constexpr uint32_t kNumStoreBoxes = 8;
     static constexpr uint32_t kOffStore = kOffB + kNumStages * SMEM_B_SIZE_PER_STAGE;
     static constexpr uint32_t kStoreBytes =
-        (kOffStore + kNumStoreBoxes * kStoreBoxBytes + 2048 <= 232448 && kOffStore % 1024 == 0) ? kNumStoreBoxes * kStoreBoxBytes : 0;
+        (kOffStore + kNumStoreBoxes * kStoreBoxBytes + 2048 <= 232448) ? kNumStoreBoxes * kStoreBoxBytes : 0;
     static constexpr uint32_t kOffBarriers = kOffStore + kStoreBytes;
     // ring full/empty, TMEM full/empty per buffer and column half
     static constexpr uint32_t kNumBarriers = 2 * kNumStages + 4 * kNumTmemBufs;
@@ -220,7 +220,7 @@ struct GemmSmemLayout {
 template <uint32_t BLOCK_N, uint32_t kNumStages, GemmType kGemmType, typename out_t>
 __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     fp8_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tensor_map_a,
-                    const __grid_constant__ CUtensorMap tensor_map_b, const __grid_constant__ CUtensorMap tensor_map_d) {
+                    const __grid_constant__ CUtensorMap tensor_map_b) {
 #if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ >= 1000)
     using L = GemmSmemLayout<BLOCK_N, kNumStages>;
     using Sched = Scheduler<kGemmType, kBlockM, BLOCK_N>;
@@ -248,11 +248,10 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
 #define YAN_PROMO_SCALE_DEPTH 4
 #endif
     constexpr uint32_t kScaleDepth = YAN_PROMO_SCALE_DEPTH;
-    // bf16 / fp32 output through the staging boxes and TMA stores (see GemmSmemLayout).  The masked grouped kind keeps
-    // register stores: its row limit is per group, which a tensor map cannot clip.
-    constexpr bool kStagedStore = L::kStoreBytes != 0 && sizeof(out_t) >= 2 && kGemmType != GemmType::GroupedMasked &&
-                                  kNumMathWarps == L::kNumStoreBoxes && (kColsPerWG * sizeof(out_t)) % 128 == 0;
-    constexpr uint32_t kStoreCols = 128 / (sizeof(out_t) >= 2 ? sizeof(out_t) : 2);  // columns per 128-byte box row
+    // bf16 / fp32 output through the staging boxes (see GemmSmemLayout) when a warpgroup's columns are whole 64-byte pieces.
+    constexpr bool kStagedStore = L::kStoreBytes != 0 && sizeof(out_t) >= 2 && kNumMathWarps == L::kNumStoreBoxes &&
+                                  (kColsPerWG * sizeof(out_t)) % 64 == 0;
+    constexpr uint32_t kStoreCols = 64 / (sizeof(out_t) >= 2 ? sizeof(out_t) : 2);  // columns per 64-byte box row
     // Half-width MMA streams: each warpgroup's columns are produced and recycled on their own barriers.
     constexpr bool kSplitHalves = (YAN_PROMO_SPLIT_HALVES != 0);
     constexpr uint32_t kNumHalves = kSplitHalves ? 2 : 1;
@@ -275,7 +274,6 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     if (warp_idx == 0 && lane_idx == 0) {
         ptx::tma_prefetch_desc(&tensor_map_a);
         ptx::tma_prefetch_desc(&tensor_map_b);
-        if constexpr (kStagedStore) ptx::tma_prefetch_desc(&tensor_map_d);
     }
     if (warp_idx == 1 && lane_idx == 0) {
 #pragma unroll
@@ -549,17 +547,20 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
             }
             if constexpr (kStagedStore) {
                 if (alive) {
-                    // Lane r fills row r of the warp's box; 16-byte chunk j of a row sits at chunk j ^ (r % 8), the
-                    // 128-byte swizzle the tensor map expects.  Rows past the matrix hold zeros and are clipped by the store.
-                    uint8_t* box = smem + L::kOffStore + (warp_idx - 4) * L::kStoreBoxBytes;
-                    const uint32_t row_addr = ptx::smem_u32(box) + lane_idx * 128u;
+                    // Lane r fills row r (64 bytes) of the warp's box; 16-byte chunk j of a row sits at chunk
+                    // j ^ ((r / 2) % 4), which keeps both the row-wise writes and the read-back free of bank conflicts.
+                    const uint32_t box = ptx::smem_u32(smem + L::kOffStore + (warp_idx - 4) * L::kStoreBoxBytes);
+                    const uint32_t row_addr = box + lane_idx * 64u;
+                    constexpr uint32_t kElemsPerChunk = 16 / sizeof(out_t);
+                    const uint32_t tile_row0 = sched.get_row_base(m_block_idx) + quarter * 32u;
+                    const uint32_t row_limit = sched.get_row_limit();
+                    out_t* out_base = reinterpret_cast<out_t*>(p.out);
 #pragma unroll
                     for (uint32_t pass = 0; pass < kColsPerWG / kStoreCols; ++pass) {
-                        if (lane_idx == 0) ptx::tma_store_wait_read<0>();  // the previous store has read the box
-                        __syncwarp();
+                        __syncwarp();  // the read-back of the previous pass is over
 #pragma unroll
-                        for (uint32_t j = 0; j < 8; ++j) {
-                            const float* a = acc + pass * kStoreCols + j * (16 / sizeof(out_t));
+                        for (uint32_t j = 0; j < 4; ++j) {
+                            const float* a = acc + pass * kStoreCols + j * kElemsPerChunk;
                             uint4 v;
                             if constexpr (sizeof(out_t) == 2) {
                                 __nv_bfloat162 t0 = __floats2bfloat162_rn(a[0], a[1]), t1 = __floats2bfloat162_rn(a[2], a[3]);
@@ -572,15 +573,18 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
                                 v = make_uint4(__float_as_uint(a[0]), __float_as_uint(a[1]), __float_as_uint(a[2]),
                                                __float_as_uint(a[3]));
                             }
-                            ptx::st_shared_v4(row_addr + ((j ^ (lane_idx & 7u)) << 4), v);
+                            ptx::st_shared_v4(row_addr + ((j ^ ((lane_idx >> 1) & 3u)) << 4), v);
                         }
-                        ptx::fence_proxy_async_smem();
                         __syncwarp();
-                        const uint32_t n_pass = n_first + pass * kStoreCols;
-                        if (lane_idx == 0 && n_pass < p.shape_n) {
-                            ptx::tma_store_2d(&tensor_map_d, box, static_cast<int32_t>(n_pass),
-                                              static_cast<int32_t>(sched.get_row_base(m_block_idx) + quarter * 32u));
-                            ptx::tma_store_commit();
+                        // read back: instruction i covers box rows 8i .. 8i+7, lane l -> row 8i + l/4, chunk l%4
+                        const uint32_t n_chunk = n_first + pass * kStoreCols + (lane_idx & 3u) * kElemsPerChunk;
+#pragma unroll
+                        for (uint32_t i = 0; i < 4; ++i) {
+                            const uint32_t r = i * 8u + (lane_idx >> 2);
+                            const uint4 v = ptx::ld_shared_v4(box + r * 64u + (((lane_idx & 3u) ^ ((r >> 1) & 3u)) << 4));
+                            const uint32_t out_row = tile_row0 + r;
+                            if (out_row < row_limit && n_chunk < p.shape_n)
+                                *reinterpret_cast<uint4*>(out_base + static_cast<size_t>(out_row) * p.ldd + n_chunk) = v;
                         }
                     }
                 }
@@ -598,9 +602,6 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
             p.clock_probe[13] = in_stores;
         }
 #endif
-        if constexpr (kStagedStore) {
-            if (lane_idx == 0) ptx::tma_store_wait<0>();  // the boxes stay valid until the last store has completed
-        }
         __syncwarp();
     }
 
@@ -681,9 +682,6 @@ struct GemmLauncher {
         bool ok = true;
         const CUtensorMap map_a = make_2d_tma_desc_u8_sw128(a.lhs, a_rows, a.k, a.k, kBlockM, ok);
         const CUtensorMap map_b = make_2d_tma_desc_u8_sw128(a.rhs, b_rows, a.k, a.k, BLOCK_N, ok);
-        CUtensorMap map_d{};  // only the kinds that stage their output read it
-        if (L::kStoreBytes != 0 && sizeof(out_t) >= 2 && kGemmType != GemmType::GroupedMasked)
-            map_d = make_2d_tma_store_desc_sw128(a.out, a_rows, a.n, a.ldd, sizeof(out_t), ok);
         if (!ok) return kTensorMapFailed;
 
         GemmParams p;
@@ -713,7 +711,7 @@ struct GemmLauncher {
             const uint32_t tiles = ceil_div(a.m, kBlockM) * ceil_div(a.n, BLOCK_N);
             grid = tiles < grid ? tiles : grid;
         }
-        kernel<<<grid, get_num_threads_per_sm<>(BLOCK_N), kSmemSize, stream>>>(p, map_a, map_b, map_d);
+        kernel<<<grid, get_num_threads_per_sm<>(BLOCK_N), kSmemSize, stream>>>(p, map_a, map_b);
         return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
     }
 };

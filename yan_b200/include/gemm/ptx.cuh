@@ -120,6 +120,12 @@ __device__ __forceinline__ void st_shared_v4(uint32_t smem_addr, const uint4& v)
                  : "memory");
 }
 
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t smem_addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_addr) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 
 template <int kPending>

@@ -55,7 +55,7 @@ struct Scheduler {
         if constexpr (kGemmType == GemmType::GroupedMasked) {
             while (true) {
                 if (curr_group_idx == num_groups) return false;
-                const uint32_t m_blocks_g = ceil_div(static_cast<uint32_t>(__ldg(grouped_layout + curr_group_idx)), BLOCK_M);
+                const uint32_t m_blocks_g = ceil_div(get_masked_rows(curr_group_idx), BLOCK_M);
                 if (next < (curr_cumsum + m_blocks_g) * num_n_blocks) {
                     swizzle(next - curr_cumsum * num_n_blocks, m_blocks_g, m_block_idx, n_block_idx);
                     return true;
@@ -87,8 +87,15 @@ struct Scheduler {
     // One past the last row the tile may store (tail guard).
     __device__ __forceinline__ uint32_t get_row_limit() const {
         if constexpr (kGemmType == GemmType::GroupedMasked)
-            return curr_group_idx * shape_m + static_cast<uint32_t>(__ldg(grouped_layout + curr_group_idx));
+            return curr_group_idx * shape_m + get_masked_rows(curr_group_idx);
         return shape_m;
+    }
+
+    // Valid rows of a masked group, clamped to [0, M_max]: the count lives in device memory where the host cannot
+    // check it, and an oversized or negative value must not make a tile store into the next group or past the output.
+    __device__ __forceinline__ uint32_t get_masked_rows(uint32_t group) const {
+        const int rows = __ldg(grouped_layout + group);
+        return static_cast<uint32_t>(min(max(rows, 0), static_cast<int>(shape_m)));
     }
 };
 

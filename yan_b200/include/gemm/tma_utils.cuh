@@ -49,26 +49,4 @@ inline CUtensorMap make_2d_tma_desc_u8_sw128(const void* base, uint64_t rows, ui
     return map;
 }
 
-// 2D row-major output matrix [rows, cols] of 2- or 4-byte elements with a row pitch of `ld` elements, written through
-// boxes of 32 rows x 128 bytes (64 bf16 or 32 fp32 columns), 128-byte swizzle.  Stores clip at `rows` and `cols`.
-inline CUtensorMap make_2d_tma_store_desc_sw128(void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t elem_bytes,
-                                                bool& ok) {
-    CUtensorMap map{};
-    EncodeTiledFn encode = get_encode_tiled();
-    if (encode == nullptr || (elem_bytes != 2 && elem_bytes != 4)) {
-        ok = false;
-        return map;
-    }
-    const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {ld * elem_bytes};
-    const cuuint32_t box[2] = {128 / elem_bytes, 32};
-    const cuuint32_t elem_strides[2] = {1, 1};
-    const CUresult r = encode(&map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
-                              base, dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) ok = false;
-    return map;
-}
-
 }  // namespace yan

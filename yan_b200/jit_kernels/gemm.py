@@ -56,11 +56,11 @@ _DEFAULT_STAGES = {32: 8, 64: 8, 96: 8, 128: 6, 160: 6, 192: 5, 224: 5, 256: 4}
 
 def get_smem_size(block_n: int, num_stages: int) -> int:
     """Dynamic shared memory of one CTA: stages x (A 128x128 + B BLOCK_Nx128 e4m3) + the output staging boxes
-    (8 x 4 KB, where the ring leaves room) + mbarriers + 1024 bytes of alignment slack (GemmSmemLayout in
+    (8 x 2 KB, where the ring leaves room) + mbarriers + 1024 bytes of alignment slack (GemmSmemLayout in
     include/gemm/fp8_gemm.cuh)."""
     num_tmem_bufs = 2 if block_n > 128 else 4
     ring = num_stages * (128 * 128 + block_n * 128)
-    store = 8 * 4096 if (ring + 8 * 4096 + 2048 <= 232448 and ring % 1024 == 0) else 0
+    store = 8 * 2048 if ring + 8 * 2048 + 2048 <= 232448 else 0
     return ring + store + (2 * num_stages + 4 * num_tmem_bufs) * 8 + 8 + 1024
 
 
