@@ -38,7 +38,17 @@ M, N, K = 8192, 28672, 8192
 WORKLOAD = "C4 column-parallel prefill GEMM M=8192 N=28672 K=8192 (B sharded along N, A replicated)"
 METRIC = "FP8 GEMM TFLOP/s (% FP8 peak); small-M HBM GB/s; 1/2/4/8-GPU scaling"
 CPU_SLAB_ROWS = 256
-GEMM_DRAM_TRAFFIC_RATIO = 1.09  # ncu: DRAM bytes / algorithmic bytes of the GEMM kernel
+# DRAM bytes / algorithmic bytes of the GEMM kernel: ncu measured 211.0 MB of dram__bytes_read+write against
+# 193.4 MB of algorithmic bytes on M=4096 N=14336 K=4096 (a case small enough to capture); L2 holds the re-used
+# operand panels at the benchmark's size too, so the same ratio is applied to its algorithmic bytes.
+GEMM_DRAM_TRAFFIC_RATIO = 1.09
+
+
+def workload_config(world: int) -> dict:
+    """The `config` object of the JSON line; both arms print the same one."""
+    return {"workload": WORKLOAD, "M": M, "N": N, "K": K, "n_per_gpu": N // world,
+            "step": "per_token_cast_to_fp8(A) + gemm_fp8_fp8_bf16_nt", "parallelism": f"n-split x{world}",
+            "l2": "per-step operands (A8 67 MB + B8 shard + D shard) exceed the 126 MB L2"}
 
 
 def load_peaks():
@@ -269,7 +279,7 @@ def bench_dense(name: str, m: int, n: int, k: int, peaks, iters: int = 10) -> di
             "quant_frac_of_measured_hbm": qbytes / tq / 1e9 / peaks["hbm_gbs"]}
 
 
-def bench_fused_epilogue(m: int, n: int, k: int, iters: int = 10) -> dict:
+def bench_fused_epilogue(m: int, n: int, k: int, iters: int = 10, peaks=None) -> dict:
     """Layer i's GEMM followed by layer i+1's activation quantizer: two kernels through a bf16 tensor against the GEMM
     whose epilogue writes e4m3 + scales directly (the outputs are bit-identical; tests/test_gemm_e4m3_out_gpu.py)."""
     import yan_b200
@@ -288,7 +298,55 @@ def bench_fused_epilogue(m: int, n: int, k: int, iters: int = 10) -> dict:
     t1 = bench_events(lambda: yan_b200.gemm_fp8_fp8_e4m3_nt(lhs, rhs, out=fused_out), num_tests=iters, flush_l2=True)
     return {"workload": f"GEMM + next layer's quantizer M={m} N={n} K={k}", "gemm_then_quantizer_us": t2 * 1e6,
             "fused_epilogue_us": t1 * 1e6, "speedup": t2 / t1,
+            "fused_TFLOP/s": 2.0 * m * n * k / t1 / 1e12,
+            "fused_frac_of_2x_measured_bf16_burst": (2.0 * m * n * k / t1 / 1e12 / (2 * peaks["bf16_tflops"])) if peaks else None,
             "hbm_bytes_saved": 2 * m * n + 2 * m * n}
+
+
+def bench_grouped(peaks, groups: int = 4, rows_per_group: int = 2048, n: int = 7168, k: int = 2048, iters: int = 10) -> dict:
+    """Grouped GEMM, contiguous layout (MoE experts): `groups` weight matrices, each applied to its own run of rows."""
+    import yan_b200
+    from yan_b200.utils import bench_events
+    m = groups * rows_per_group
+    g = torch.Generator(device="cuda").manual_seed(11)
+    a = torch.randn(m, k, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    lhs = yan_b200.per_token_cast_to_fp8(a)
+    qs, ss = [], []
+    for i in range(groups):
+        w = (torch.randn(n, k, generator=g, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        q, sc = yan_b200.per_block_cast_to_fp8(w)
+        qs.append(q)
+        ss.append(sc)
+    rhs = (torch.stack(qs).contiguous(), torch.stack(ss).contiguous())
+    m_indices = torch.arange(groups, device="cuda", dtype=torch.int32).repeat_interleave(rows_per_group).contiguous()
+    out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    t = bench_events(lambda: yan_b200.m_grouped_gemm_fp8_fp8_bf16_nt_contiguous(lhs, rhs, out, m_indices),
+                     num_tests=iters, flush_l2=True)
+    tf = 2.0 * m * n * k / t / 1e12
+    return {"workload": f"grouped GEMM (contiguous) {groups} groups x {rows_per_group} rows, N={n} K={k}", "gemm_us": t * 1e6,
+            "TFLOP/s": tf, "frac_of_2x_measured_bf16_burst": tf / (2 * peaks["bf16_tflops"]),
+            "frac_of_nominal_4.5PF": tf / 4500.0}
+
+
+def bench_sustained(step, flops_per_step: float, burst_ms: float, device_index: int, seconds: float = 2.0) -> dict:
+    """The same step back to back for about `seconds` (the power cap, not the burst clock, sets this figure), with the
+    median SM clock of the NVML samples taken inside the window."""
+    steps = max(20, int(seconds / (burst_ms / 1e3)))
+    sampler = ClockSampler(device_index, period_s=0.01)
+    torch.cuda.synchronize()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_begin = time.perf_counter()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop(t_begin, time.perf_counter())
+    ms = e0.elapsed_time(e1) / steps
+    return {"workload": f"C4 step (quantize + GEMM) back to back for {steps} steps (~{seconds:.0f} s)", "ms_per_step": ms,
+            "TFLOP/s": flops_per_step / (ms / 1e3) / 1e12, "sm_mhz_median": clocks.get("sm_mhz"),
+            "clock_samples": clocks.get("samples_in_timed_region"), "reasons": clocks.get("reasons")}
 
 
 def _time_k_split(step, dist, steps: int, m: int, n: int, k: int, flops: bool = True) -> dict:
@@ -367,6 +425,100 @@ def bench_k_split(rank: int, world: int, dist, steps: int = 10) -> dict:
             "allreduce_bytes": 2 * m * n, **results}
 
 
+def multi_gpu_parity(rank: int, world: int, dist) -> dict:
+    """Every sharded form once on a small checked case (M=512, N=1024, K=2048 per rank), before anything is timed:
+    the same code paths the timed legs use, compared with the CPU oracle's unsplit / K-split results.  Each entry
+    holds the worst figures over the ranks.  (The oracle is the checker here; nothing timed touches it.)"""
+    import yan_b200
+    from oracle import ref
+    from yan_b200.comm import gemm_allreduce as ga
+    m, n, k = 512, 1024, 2048 * world
+    threads_before = torch.get_num_threads()
+    torch.set_num_threads(max(1, (os.cpu_count() or 1) // world))  # the launcher pins its ranks to one thread
+    a, b = ref.make_inputs(m, n, k, seed=3)
+    lhs, rhs = ref.per_token_cast_to_fp8(a), ref.per_block_cast_to_fp8(b)
+    d_ref = ref.ref_gemm(lhs, rhs)
+    d_split = ref.ref_gemm_k_split(lhs, rhs, world)
+    torch.set_num_threads(threads_before)
+    out = {}
+
+    def record(name, got, want, tol, extra=None):
+        got = got.float().cpu()
+        fro = float(ref.rel_frobenius(got, want))
+        mx = float((got - want.float()).abs().max())
+        t = torch.tensor([fro, mx], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        entry = {"rel_frobenius": t[0].item(), "max_abs": t[1].item(), "tolerance": tol, "pass": bool(t[0].item() <= tol)}
+        if extra:
+            flags = torch.tensor([1.0 if v else 0.0 for v in extra.values()], device="cuda", dtype=torch.float64)
+            dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+            for key, v in zip(extra.keys(), flags.tolist()):
+                entry[key] = bool(v)
+                entry["pass"] = entry["pass"] and bool(v)
+        out[name] = entry
+
+    lhs_dev = (lhs[0].contiguous().cuda(), lhs[1].t().contiguous().cuda().t())
+    # N-split: every rank writes its own column slice of a zeroed full buffer; summing the buffers assembles D
+    full = torch.zeros(m, n, dtype=torch.bfloat16, device="cuda")
+    rhs_n = tuple(t.contiguous().cuda() for t in ga.shard_n(rhs, rank, world))
+    ga.gemm_n_split(lhs_dev, rhs_n, full, rank, world)
+    dist.all_reduce(full)
+    record("n_split", full, d_ref, 1e-3)
+    # K-split over NCCL: bf16 partials (the specified arithmetic) and fp32 partials
+    ks = k // world
+    lhs_k = yan_b200.per_token_cast_to_fp8(a[:, rank * ks:(rank + 1) * ks].contiguous().cuda())
+    rhs_k = tuple(t.contiguous().cuda() for t in ga.shard_k(rhs, rank, world))
+    res = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    ga.gemm_k_split_allreduce(lhs_k, rhs_k, res, partial_dtype=torch.bfloat16, num_chunks=2)
+    torch.cuda.synchronize()
+    record("k_split_nccl_bf16_partials", res, d_split, 2e-3)
+    ga.gemm_k_split_allreduce(lhs_k, rhs_k, res, partial_dtype=torch.float32, num_chunks=2)
+    torch.cuda.synchronize()
+    record("k_split_nccl_fp32_partials", res, d_ref, 1e-3)
+    # the peer-memory kernels: the fp32 sum of the ranks' bf16 partials in rank order, rounded once, is what the
+    # plain load/store kernel must reproduce bit for bit
+    partial = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    yan_b200.gemm_fp8_fp8_bf16_nt(lhs_k, rhs_k, partial)
+    gathered = [torch.empty_like(partial) for _ in range(world)]
+    dist.all_gather(gathered, partial)
+    acc = torch.zeros(m, n, dtype=torch.float32, device="cuda")
+    for g in gathered:
+        acc += g.float()
+    rank_order_sum = acc.to(torch.bfloat16)
+    try:
+        from yan_b200.comm import TwoShotAllreduce
+        for name, in_switch, tol in (("two_shot", False, 2e-3), ("in_switch", True, 6e-3)):
+            try:
+                comm = TwoShotAllreduce(m, n, in_switch=in_switch)
+            except Exception as e:
+                out["k_split_" + name] = {"unavailable": f"{type(e).__name__}: {e}"[:160]}
+                continue
+            for chunks in (1, 2):
+                got = ga.gemm_k_split_two_shot(lhs_k, rhs_k, comm, num_chunks=chunks)
+                torch.cuda.synchronize()
+                extra = None if in_switch else {"bit_exact_vs_fp32_rank_order_sum": bool(torch.equal(got, rank_order_sum))}
+                record(f"k_split_{name}_{chunks}_chunk" + ("s" if chunks > 1 else ""), got, d_split, tol, extra)
+            # a row range alone: rows outside keep this rank's own partial
+            comm.buffer.copy_(partial)
+            comm.reduce_rows(128, 384, num_ctas=7)
+            torch.cuda.synchronize()
+            inside = comm.buffer[128:384]
+            untouched = bool(torch.equal(comm.buffer[:128], partial[:128]) and torch.equal(comm.buffer[384:], partial[384:]))
+            extra = {"rows_outside_untouched": untouched}
+            if not in_switch:
+                extra["bit_exact_vs_fp32_rank_order_sum"] = bool(torch.equal(inside, rank_order_sum[128:384]))
+            record(f"{name}_reduce_rows_128_384", inside, d_split[128:384], tol, extra)
+            comm.close()
+    except Exception as e:
+        out["peer_memory"] = {"unavailable": f"{type(e).__name__}: {e}"[:160]}
+    status = torch.tensor([float(yan_b200.read_device_status())], device="cuda", dtype=torch.float64)
+    dist.all_reduce(status, op=dist.ReduceOp.MAX)
+    out["device_status"] = int(status.item())
+    out["all_pass"] = all(v.get("pass", True) for v in out.values() if isinstance(v, dict)) and out["device_status"] == 0
+    out["case"] = f"M={m} N={n} K={k} ({world} ranks; oracle: CPU dequantize-and-matmul, K-split restated for the split forms)"
+    return out
+
+
 def cpu_reference_step(a_slab, rhs_cpu):
     """The CPU dequantize-and-matmul path on one slab: quantize A, dequantize both, fp32 matmul, bf16."""
     from oracle import ref
@@ -387,6 +539,9 @@ def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torch.distributed.run exports OMP_NUM_THREADS=1 to its ranks: use the box's cores at every N all the same
+    torch.set_num_threads(args.cpu_threads if args.cpu_threads > 0 else (os.cpu_count() or 1))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     a, rhs = make_cpu_inputs()
     for _ in range(max(1, min(args.warmup, 2))):
         cpu_reference_step(a, rhs)
@@ -402,7 +557,7 @@ def run_reference(args) -> None:
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32 (dequantized e4m3)", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "M": M, "N": N, "K": K},
+            "config": workload_config(world),
             "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -431,11 +586,15 @@ def run_ours(args) -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    parity = multi_gpu_parity(rank, world, dist) if world > 1 else None
+
     for _ in range(args.warmup):
         step()
     barrier()
 
     # ---- timed region: exactly K steps; per-kernel events on the launching (current) stream ----
+    probe = torch.zeros(16, dtype=torch.int64, device="cuda")
+    yan_b200.set_clock_probe(probe)  # CTA 0 of every GEMM launch stamps clock64 / globaltimer at start and end
     sampler = ClockSampler(local)
     sampler.start()
     time.sleep(0.05)
@@ -454,6 +613,10 @@ def run_ours(args) -> None:
     t_end.record()
     barrier()
     clocks = sampler.stop(wall_begin, time.perf_counter())
+    yan_b200.set_clock_probe(None)
+    # the clock the last timed GEMM launch really ran at (a launch of a millisecond or two falls between NVML samples)
+    clocks["gemm_kernel_sm_mhz"] = yan_b200.effective_sm_clock_mhz(probe)
+    clocks["gemm_kernel_sm_mhz_source"] = "clock64 delta / globaltimer delta of CTA 0, last timed launch"
     elapsed_ms = t_start.elapsed_time(t_end)
     quant_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
     gemm_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
@@ -508,9 +671,6 @@ def run_ours(args) -> None:
     gemm_flops = 2.0 * M * n_local * K
     achieved = gemm_flops / (gemm_ms / 1e3) / 1e12
     fp8_peak = 2.0 * peaks["bf16_tflops"]
-    # DRAM traffic of one launch: ncu (profiles/fp8_gemm_kernel_4096x14336x4096.md) measured 211.0 MB of
-    # dram__bytes_read+write against 193.4 MB of algorithmic bytes on a case small enough to capture; the same
-    # ratio is applied to this launch's algorithmic bytes (L2 holds the re-used operand panels in both cases).
     algo_bytes = M * K + 4 * M * (K // 128) + n_local * K + 4 * (n_local // 128) * (K // 128) + 2 * M * n_local
     traffic = GEMM_DRAM_TRAFFIC_RATIO * algo_bytes
     roofline = {"kernel": "fp8_gemm_kernel<BLOCK_N=256>", "bound": "tensor", "achieved": achieved, "peak": fp8_peak,
@@ -527,9 +687,7 @@ def run_ours(args) -> None:
     line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "e4m3 (fp32 accumulate, bf16 out)", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "M": M, "N": N, "K": K, "n_per_gpu": n_local,
-                       "step": "per_token_cast_to_fp8(A) + gemm_fp8_fp8_bf16_nt", "parallelism": f"n-split x{world}",
-                       "l2": "per-step operands (A8 67 MB + B8 shard + D shard) exceed the 126 MB L2", "device": dev_name},
+            "config": workload_config(world), "device": dev_name,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": a_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
                     "single_step_latency_ms": e2e_serial_ms,
@@ -537,7 +695,13 @@ def run_ours(args) -> None:
                             "host memory and D out to pinned host memory; copies of one step overlap the kernels of the "
                             "next (2 device slots, 3 streams)"},
             "gpu_launches": 2 * args.steps, "clocks": clocks, "roofline": roofline}
+    if parity is not None:
+        line["parity"] = parity
 
+    sustained = None
+    if world == 1 and not args.no_extras:
+        sustained = bench_sustained(step, flops_total, ms_per_step, local)
+        sustained["frac_of_2x_sustained_bf16"] = sustained["TFLOP/s"] / (2.0 * peaks["bf16_tflops_sustained"])
     del a_host, out_host, out_hosts, pipe, a_dev, out, lhs, rhs, a
     torch.cuda.empty_cache()
 
@@ -551,8 +715,12 @@ def run_ours(args) -> None:
             extras.append(bench_decode(m_small, peaks))
         extras.append(bench_dense("C3 mid-size projection", 4096, 7168, 18432, peaks))
         extras.append(bench_dense("C1 CPU-runnable", 256, 1024, 1024, peaks))
-        extras.append(bench_fused_epilogue(4096, 7168, 18432))
-        extras.append(bench_fused_epilogue(8192, 7168, 2048))
+        extras.append(bench_fused_epilogue(4096, 7168, 18432, peaks=peaks))
+        extras.append(bench_fused_epilogue(8192, 7168, 2048, peaks=peaks))
+        extras.append(bench_fused_epilogue(M, N, K, iters=5, peaks=peaks))
+        extras.append(bench_grouped(peaks))
+        if sustained is not None:
+            extras.append(sustained)
         line["other_workloads"] = extras
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         a_cpu, rhs_cpu = make_cpu_inputs()
@@ -608,6 +776,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the decode / C3 / C1 side measurements")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-threads", type=int, default=0, help="host threads of the CPU arm (0 = all cores)")
     ap.add_argument("--case", default=None, metavar="M,N,K[,BLOCK_N]",
                     help="profiling aid: run quantize + GEMM of one shape `--steps` times on one GPU and print its timing")
     args = ap.parse_args()

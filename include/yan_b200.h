@@ -234,6 +234,14 @@ void yan_b200_set_clock_probe(void* device_buffer);
 /* Sets the bound (nanoseconds, default 2e9) of every device-side wait of later GEMM launches. */
 void yan_b200_set_wait_timeout_ns(unsigned long long timeout_ns);
 
+/* Sets the bound (nanoseconds, default 1e10) of the waits between ranks in later allreduce launches.  It is separate
+ * from the bound above because ranks drift apart by seconds for ordinary host-side reasons.  When such a wait runs out
+ * the kernel leaves the data alone, records YAN_B200_DEVICE_TIMEOUT in the status word and still keeps its counters
+ * and epoch flags in step with the host, so a later launch is not poisoned; the buffer's contents of that call are
+ * undefined.  No reference counterpart (nvshmem's tile collectives wait without a bound,
+ * comm/gemm_allreduce.cu:403-410). */
+void yan_b200_set_collective_timeout_ns(unsigned long long timeout_ns);
+
 #ifdef __cplusplus
 }
 #endif

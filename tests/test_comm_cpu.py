@@ -185,3 +185,57 @@ def test_two_shot_slices_partition_the_range():
                 covered.append((first, last))
             assert covered[0][0] == 0 and covered[-1][1] == count
             assert all(covered[i][1] == covered[i + 1][0] for i in range(world - 1))
+
+
+class _ModelRank:
+    """Device half of one rank's ordering state as the allreduce kernels keep it (PeerSignals in
+    include/comm/peer_allreduce.cuh), reduced to what the bookkeeping needs: a cumulative CTA counter and the epoch it
+    has published as done.  `timed_out` models a launch whose entry wait ran out on every CTA."""
+
+    def __init__(self):
+        self.cta_counter = 0
+        self.done_epoch = 0
+
+    def launch(self, epoch, counter_target, ctas, timed_out=False, counts_on_timeout=True):
+        published = False
+        for _ in range(ctas):
+            if timed_out and not counts_on_timeout:
+                continue  # the old behaviour: a CTA that gave up at entry returned without counting itself
+            self.cta_counter = (self.cta_counter + 1) & 0xFFFFFFFF
+            if self.cta_counter == counter_target:
+                self.done_epoch = epoch
+                published = True
+        return published
+
+
+def test_collective_clock_survives_a_timed_out_launch():
+    from yan_b200.comm.peer_memory import CollectiveClock
+    clock, device = CollectiveClock(), _ModelRank()
+    assert device.launch(*clock.next_launch(148), 148)
+    # a launch whose entry wait ran out still counts its CTAs and publishes its epoch ...
+    assert device.launch(*clock.next_launch(24), 24, timed_out=True)
+    # ... so the launches after it reach their targets again
+    for ctas in (148, 7, 64):
+        epoch, target = clock.next_launch(ctas)
+        assert device.launch(epoch, target, ctas) and device.done_epoch == epoch
+    assert device.cta_counter == clock.cta_count
+
+    # the behaviour this replaces: the counter falls behind for good and no later launch publishes
+    clock, device = CollectiveClock(), _ModelRank()
+    device.launch(*clock.next_launch(24), 24, timed_out=True, counts_on_timeout=False)
+    assert not device.launch(*clock.next_launch(24), 24)
+
+    # reset() starts both halves over (the device half is zeroed by TwoShotAllreduce.reset)
+    clock.reset()
+    device = _ModelRank()
+    epoch, target = clock.next_launch(5)
+    assert (epoch, target) == (1, 5) and device.launch(epoch, target, 5)
+
+
+def test_collective_clock_wraps_without_using_epoch_zero():
+    from yan_b200.comm.peer_memory import CollectiveClock
+    clock = CollectiveClock()
+    clock.epoch = 0xFFFFFFFF
+    clock.cta_count = 0xFFFFFFF0
+    epoch, target = clock.next_launch(32)
+    assert epoch == 1 and target == 0x10

@@ -68,6 +68,11 @@ def test_fp8_gemm_through_jit_template(cuda_lib, tmp_path, monkeypatch):
         torch.cuda.synchronize()
         assert ref.rel_frobenius(out.cpu(), ref.ref_gemm(lhs, rhs)) <= 1e-3
         assert any(d.startswith("kernel.gemm_fp8_fp8_bf16_nt.") for d in os.listdir(os.path.join(tmp_path, "cache")))
+        # the JIT-compiled library has a status word of its own, which the package-level read covers
+        from yan_b200.jit_kernels import gemm as gemm_module
+        used = [r for r in gemm_module._jit_runtimes_used.values() if str(tmp_path) in r.path]
+        assert used and hasattr(used[0].lib, "yan_jit_read_device_status")
+        assert used[0].read_device_status() == 0 and yan_b200.read_device_status() == 0
     finally:
         compiler.get_default_user_dir.cache_clear()
 

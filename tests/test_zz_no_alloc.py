@@ -48,10 +48,8 @@ def test_static_scratch_matches_workspace_entry_twice_in_a_row(cuda_lib):
         rhs = ref.per_block_cast_to_fp8(b)
         out_static, out_ws = _both(a.cuda(), rhs[0].cuda(), rhs[1].cuda())
         assert not torch.isnan(out_static.float()).any()
-        fro = ref.rel_frobenius(out_static.cpu(), out_ws.cpu())
-        assert fro <= REL_FRO_TOL, f"call {seed}: static vs workspace rel Frobenius {fro}"
-        bound = ref.bf16_ulp_at(float(out_ws.float().abs().max()))
-        assert ref.max_abs_err(out_static.cpu(), out_ws.cpu()) <= bound
+        # the two entry points run the same two kernels on the same inputs: nothing may differ
+        assert torch.equal(out_static, out_ws), f"call {seed}: static and workspace entry points differ"
         # and both agree with the CPU oracle
         d_ref = ref.ref_gemm(ref.per_token_cast_to_fp8(a), rhs)
         assert ref.rel_frobenius(out_static.cpu(), d_ref) <= REL_FRO_TOL

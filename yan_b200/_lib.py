@@ -47,6 +47,7 @@ SIGNATURES = {
     "yan_b200_set_programmatic_dependent_launch": (None, [_I]),
     "yan_b200_set_wait_timeout_ns": (None, [ctypes.c_ulonglong]),
     "yan_b200_set_clock_probe": (None, [_P]),
+    "yan_b200_set_collective_timeout_ns": (None, [ctypes.c_ulonglong]),
 }
 
 # YAN_B200_STATIC_SCRATCH_MAX_ELEMENTS of include/yan_b200.h

@@ -130,6 +130,29 @@ class MulticastSharedTensor:
         self._handle = None
 
 
+class CollectiveClock:
+    """Host half of the allreduce kernels' ordering state: the epoch the next launch announces to its peers and the
+    value this rank's CTA counter reaches when that launch's last CTA is through.  The device half lives in the
+    signal block (`PeerSignals` in include/comm/peer_allreduce.cuh).  Every launch advances both halves by the same
+    amounts whether its waits ran out or not, so one timed-out call does not poison the next; `reset` starts over
+    after the signal block has been zeroed."""
+
+    def __init__(self) -> None:
+        self.epoch = 0
+        self.cta_count = 0
+
+    def next_launch(self, ctas: int):
+        """(epoch, counter_target) of a launch with `ctas` CTAs."""
+        assert ctas > 0
+        self.epoch = (self.epoch + 1) & 0xFFFFFFFF or 1  # 0 means "the caller orders the ranks"
+        self.cta_count = (self.cta_count + ctas) & 0xFFFFFFFF
+        return self.epoch, self.cta_count
+
+    def reset(self) -> None:
+        self.epoch = 0
+        self.cta_count = 0
+
+
 class TwoShotAllreduce:
     """In-place sum over the ranks of a peer-shared bf16 matrix [M, N] (`buffer`): the GEMM writes its partial product
     into `buffer`, `reduce_rows` leaves the sum of all ranks' partials there on every rank.
@@ -158,8 +181,7 @@ class TwoShotAllreduce:
         self.device_barriers = device_barriers
         sms = torch.cuda.get_device_properties(self.buffer.device).multi_processor_count
         self.num_ctas = num_ctas or sms  # one CTA per SM saturates the links (measured)
-        self._epoch = 0
-        self._cta_count = 0
+        self._clock = CollectiveClock()
         self._token = torch.zeros(1, dtype=torch.float32, device="cuda")
 
     def reduce_rows(self, row_begin: int = 0, row_end: Optional[int] = None, num_ctas: Optional[int] = None,
@@ -177,14 +199,23 @@ class TwoShotAllreduce:
         else:
             name, target = "yan_b200_allreduce_bf16_two_shot", self._data
         if self.device_barriers:
-            self._epoch += 1
-            self._cta_count = (self._cta_count + ctas) & 0xFFFFFFFF
-            _lib.call(name, target, self._signals, self.world, self.rank, begin, count, self._epoch, self._cta_count,
+            epoch, counter_target = self._clock.next_launch(ctas)
+            _lib.call(name, target, self._signals, self.world, self.rank, begin, count, epoch, counter_target,
                       ctas, int(exclusive_sms), stream)
         else:
             dist.all_reduce(self._token, group=self.group)  # every rank's partial is complete
             _lib.call(name, target, None, self.world, self.rank, begin, count, 0, 0, ctas, int(exclusive_sms), stream)
             dist.all_reduce(self._token, group=self.group)  # every rank's stores have landed
+
+    def reset(self) -> None:
+        """Collective: every rank calls it after a reported wait expiry (or whenever the ranks want a clean slate).
+        Waits for all ranks' work, zeroes every signal block and restarts the epochs."""
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        self._arena.local[self.m * self.n * 2:].zero_()
+        self._clock.reset()
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
 
     def close(self) -> None:
         self._arena.close()

@@ -20,6 +20,9 @@ namespace {
 __device__ int g_status_word = 0;
 
 unsigned long long g_timeout_ns = 2000000000ull;
+// The waits between ranks have a bound of their own: ranks of one job drift apart by seconds for ordinary reasons
+// (first-call module loading, a garbage collection, a stalled data loader), which no wait inside one kernel does.
+unsigned long long g_collective_timeout_ns = 10000000000ull;
 int g_programmatic_launch = 0;
 long long* g_clock_probe = nullptr;
 
@@ -90,7 +93,7 @@ inline void set_rc(int* rc, int v) {
 // machine better (few tiles, or a last wave of 256-wide tiles that is nearly empty).
 int choose_block_n(int m, int n, int num_sms) {
     static const struct { int bn; double tile_cost; } candidates[8] = {
-        {256, 1.000}, {224, 0.985}, {192, 0.869}, {160, 0.823}, {128, 0.672}, {96, 0.62}, {64, 0.50}, {32, 0.42}};
+        {256, 1.000}, {224, 1.02}, {192, 0.83}, {160, 0.79}, {128, 0.63}, {96, 0.62}, {64, 0.50}, {32, 0.47}};
     int best = 256;
     double best_cost = -1.0;
     for (const auto& c : candidates) {
@@ -352,6 +355,11 @@ YAN_EXPORT void yan_b200_read_device_status(int* status, int reset, int* return_
     if (status == nullptr) return set_rc(return_code, yan::kBadArgument);
     int* word = status_word_of_current_device();
     if (word == nullptr) return set_rc(return_code, yan::kLaunchFailed);
+    // cudaMemcpy alone only orders against the legacy default stream; kernels on non-blocking streams must finish too
+    if (cudaDeviceSynchronize() != cudaSuccess) {
+        cudaGetLastError();
+        return set_rc(return_code, yan::kLaunchFailed);
+    }
     if (cudaMemcpy(status, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
         cudaGetLastError();
         return set_rc(return_code, yan::kLaunchFailed);
@@ -446,7 +454,7 @@ YAN_EXPORT void yan_b200_allreduce_bf16_two_shot(void* const* data, void* const*
     a.num_ctas = num_ctas;
     a.exclusive = exclusive_sms != 0;
     a.status = status_word_of_current_device();
-    a.timeout_ns = g_timeout_ns;
+    a.timeout_ns = g_collective_timeout_ns;
     set_rc(return_code, yan::launch_two_shot_allreduce_bf16(a, static_cast<cudaStream_t>(stream)));
 }
 
@@ -468,7 +476,7 @@ YAN_EXPORT void yan_b200_allreduce_bf16_in_switch(void* multicast, void* const* 
     a.num_ctas = num_ctas;
     a.exclusive = exclusive_sms != 0;
     a.status = status_word_of_current_device();
-    a.timeout_ns = g_timeout_ns;
+    a.timeout_ns = g_collective_timeout_ns;
     set_rc(return_code, yan::launch_two_shot_allreduce_bf16(a, static_cast<cudaStream_t>(stream)));
 }
 
@@ -478,6 +486,10 @@ YAN_EXPORT void yan_b200_set_clock_probe(void* device_buffer) { g_clock_probe = 
 
 YAN_EXPORT void yan_b200_set_wait_timeout_ns(unsigned long long timeout_ns) {
     g_timeout_ns = timeout_ns == 0 ? 1 : timeout_ns;
+}
+
+YAN_EXPORT void yan_b200_set_collective_timeout_ns(unsigned long long timeout_ns) {
+    g_collective_timeout_ns = timeout_ns == 0 ? 1 : timeout_ns;
 }
 
 }  // extern "C"

@@ -118,11 +118,13 @@ __device__ __forceinline__ bool enter_collective(const PeerPtrs& signals, PeerSi
 }
 
 // Exit barrier: after a system-scope fence by every thread, the last CTA of the grid tells every peer that this rank's
-// stores are done and waits for the same from all.
+// stores are done and waits for the same from all.  A CTA whose entry wait ran out (`entered` false) still counts
+// itself and the last one still publishes `done`, so the CTA counter and the epoch flags stay in step with the host's
+// bookkeeping and the next launch works; it does not wait for the peers a second time.
 template <int W>
 __device__ __forceinline__ void leave_collective(const PeerPtrs& signals, PeerSignals* my_signals, int rank,
                                                  uint32_t epoch, uint32_t counter_target, int* status,
-                                                 unsigned long long timeout_ns) {
+                                                 unsigned long long timeout_ns, bool entered = true) {
     __shared__ int s_last;
     comm_detail::fence_sys();
     __syncthreads();
@@ -131,7 +133,7 @@ __device__ __forceinline__ void leave_collective(const PeerPtrs& signals, PeerSi
     if (s_last && threadIdx.x < W) {
         comm_detail::fence_sys();
         comm_detail::st_release_sys(&static_cast<PeerSignals*>(signals.p[threadIdx.x])->done[rank], epoch);
-        if (!comm_detail::wait_flag(&my_signals->done[threadIdx.x], epoch, timeout_ns) && status != nullptr)
+        if (entered && !comm_detail::wait_flag(&my_signals->done[threadIdx.x], epoch, timeout_ns) && status != nullptr)
             atomicCAS(status, 0, (static_cast<int>(kDeviceTimeout) << 8) | 17);
     }
 }
@@ -144,8 +146,11 @@ __global__ void __launch_bounds__(kThreads)
                                    int* status, const unsigned long long timeout_ns) {
     static_assert(W >= 2 && W <= kMaxPeers, "one NVSwitch box");
     PeerSignals* my_signals = static_cast<PeerSignals*>(signals.p[rank]);
-    // inputs incomplete after the bound: leave the buffers alone (the host reads the status word)
-    if (epoch != 0 && !enter_collective<W>(signals, my_signals, rank, epoch, status, timeout_ns)) return;
+    // inputs incomplete after the bound: leave the buffers alone (the host reads the status word), keep the counters right
+    if (epoch != 0 && !enter_collective<W>(signals, my_signals, rank, epoch, status, timeout_ns)) {
+        leave_collective<W>(signals, my_signals, rank, epoch, counter_target, status, timeout_ns, false);
+        return;
+    }
 
     // ---- this rank's slice: loads from all W buffers, one fp32 sum in rank order, stores to all W buffers ----
     const size_t per_rank = (vec_count + W - 1) / W;
@@ -203,7 +208,10 @@ __global__ void __launch_bounds__(kThreads)
                                     const size_t vec_count, const uint32_t epoch, const uint32_t counter_target,
                                     int* status, const unsigned long long timeout_ns) {
     PeerSignals* my_signals = static_cast<PeerSignals*>(signals.p[rank]);
-    if (epoch != 0 && !enter_collective<W>(signals, my_signals, rank, epoch, status, timeout_ns)) return;
+    if (epoch != 0 && !enter_collective<W>(signals, my_signals, rank, epoch, status, timeout_ns)) {
+        leave_collective<W>(signals, my_signals, rank, epoch, counter_target, status, timeout_ns, false);
+        return;
+    }
 
     const size_t per_rank = (vec_count + W - 1) / W;
     const size_t first = vec_begin + static_cast<size_t>(rank) * per_rank;

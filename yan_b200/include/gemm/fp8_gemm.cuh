@@ -723,6 +723,52 @@ struct GemmLauncher {
 // compatibility and must be 1: this kernel never multicasts.  The scale and output "descriptors" carry plain pointers because the kernel
 // reads scales with ordinary loads and writes D with 16-byte stores.
 // ---------------------------------------------------------------------------------------------
+// A kernel library compiled by the JIT layer (-DYAN_JIT_KERNEL) has a status word and a wait bound of its own, read
+// and set through two extra exports next to `launch`; the prebuilt library passes its own through GemmArgs instead.
+#ifdef YAN_JIT_KERNEL
+namespace jit_state {
+__device__ int g_status_word = 0;
+inline unsigned long long g_timeout_ns = 2000000000ull;
+inline int* status_word() {
+    static int* ptr[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (ptr[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        ptr[dev] = static_cast<int*>(p);
+    }
+    return ptr[dev];
+}
+}  // namespace jit_state
+
+// 0 on success; *status = 0 or (kDeviceTimeout << 8) | site.  Synchronises the device.
+extern "C" __attribute__((visibility("default"))) inline __attribute__((used)) int yan_jit_read_device_status(int* status,
+                                                                                                               int reset) {
+    int* word = jit_state::status_word();
+    if (status == nullptr || word == nullptr) return kLaunchFailed;
+    if (cudaDeviceSynchronize() != cudaSuccess || cudaMemcpy(status, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        cudaGetLastError();
+        return kLaunchFailed;
+    }
+    if (reset != 0 && *status != 0) {
+        const int zero = 0;
+        if (cudaMemcpy(word, &zero, sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess) {
+            cudaGetLastError();
+            return kLaunchFailed;
+        }
+    }
+    return kOk;
+}
+extern "C" __attribute__((visibility("default"))) inline __attribute__((used)) void yan_jit_set_wait_timeout_ns(
+    unsigned long long timeout_ns) {
+    jit_state::g_timeout_ns = timeout_ns == 0 ? 1 : timeout_ns;
+}
+#endif
+
 struct ScalesADesc {
     const float* ptr;
     uint32_t ld;
@@ -778,6 +824,10 @@ public:
         a.k = SHAPE_K;
         a.num_groups = kNumGroups;
         a.num_sms = num_sms;
+#ifdef YAN_JIT_KERNEL
+        a.status = jit_state::status_word();
+        a.timeout_ns = jit_state::g_timeout_ns;
+#endif
         return Launcher::launch(a, stream);
     }
 };

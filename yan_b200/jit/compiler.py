@@ -143,7 +143,8 @@ def get_arch_flag() -> str:
 def get_flags(extra_flags: Iterable[str] = ()) -> list:
     ptxas = "--ptxas-options=--register-usage-level=10" + (",--verbose" if "YAN_PTXAS_VERBOSE" in os.environ else "")
     cxx = ["-fPIC", "-O3", "-Wno-deprecated-declarations", "-Wno-abi"]
-    return ["-std=c++20", "-O3", "--expt-relaxed-constexpr", "--expt-extended-lambda", "-lineinfo", get_arch_flag(),
+    # YAN_JIT_KERNEL: headers add the per-library status word and its two exports (include/gemm/fp8_gemm.cuh)
+    return ["-std=c++20", "-O3", "-DYAN_JIT_KERNEL=1", "--expt-relaxed-constexpr", "--expt-extended-lambda", "-lineinfo", get_arch_flag(),
             "-shared", ptxas, "--diag-suppress=177,174,940", f"--compiler-options={','.join(cxx)}", *extra_flags]
 
 

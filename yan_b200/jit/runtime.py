@@ -50,6 +50,31 @@ class Runtime:
         self.lib.launch(*cargs, ctypes.byref(return_code))
         return return_code.value
 
+    def read_device_status(self, reset: bool = True) -> int:
+        """Status word of this kernel library (0 = no bounded device-side wait ran out), for libraries whose headers
+        export one; 0 for the others.  Synchronises the device."""
+        if self.lib is None:
+            return 0
+        try:
+            fn = self.lib.yan_jit_read_device_status
+        except AttributeError:
+            return 0
+        status = ctypes.c_int(0)
+        rc = fn(ctypes.byref(status), int(reset))
+        if rc != 0:
+            raise RuntimeError(f"yan_jit_read_device_status failed with code {rc}")
+        return status.value
+
+    def set_wait_timeout_ns(self, timeout_ns: int) -> None:
+        if self.lib is None:
+            self._load()
+        try:
+            fn = self.lib.yan_jit_set_wait_timeout_ns
+        except AttributeError:
+            return
+        fn.argtypes = [ctypes.c_ulonglong]
+        fn(int(timeout_ns))
+
 
 class RuntimeCache:
     def __init__(self) -> None:

@@ -65,7 +65,7 @@ def get_smem_size(block_n: int, num_stages: int) -> int:
 
 
 # time of one tile relative to a 256-wide one (measured; see choose_block_n in csrc/capi.cu)
-_TILE_COST = {256: 1.000, 224: 0.985, 192: 0.869, 160: 0.823, 128: 0.672, 96: 0.62, 64: 0.50, 32: 0.42}
+_TILE_COST = {256: 1.000, 224: 1.02, 192: 0.83, 160: 0.79, 128: 0.63, 96: 0.62, 64: 0.50, 32: 0.47}
 
 
 def get_best_configs(m: int, n: int, k: int, num_sms: int) -> Tuple[int, int, int]:
@@ -140,6 +140,7 @@ def gemm_fp8_fp8_bf16_nt(lhs: Tuple[torch.Tensor, torch.Tensor], rhs: Tuple[torc
         rc = runtime(*args)
         if rc != 0:
             raise _lib.YanB200Error('gemm_fp8_fp8_bf16_nt[jit]', rc, 'see ReturnCode in include/gemm/utils.cuh')
+        _jit_runtimes_used[runtime.path] = runtime
         return
     _lib.call("yan_b200_gemm_fp8_fp8_bf16_nt", lhs_q.data_ptr(), lhs_scales.data_ptr(), rhs_q.data_ptr(),
               rhs_scales.data_ptr(), out.data_ptr(), m, n, k, out.stride(0), _stream_ptr(), num_sms, block_n)
@@ -291,8 +292,18 @@ def effective_sm_clock_mhz(buffer: torch.Tensor) -> float:
     return 1000.0 * (v[2] - v[0]) / max(v[3] - v[1], 1)
 
 
+_jit_runtimes_used = {}  # kernel libraries the JIT route has launched: each has a status word of its own
+
+
 def read_device_status(reset: bool = True) -> int:
-    """Synchronises and returns the device status word (0 = no bounded wait ever ran out)."""
+    """Synchronises and returns the device status word (0 = no bounded wait ever ran out): the prebuilt library's, or,
+    if that is clean, the first non-zero word of a JIT-compiled GEMM library this process has launched."""
     status = ctypes.c_int(0)
     _lib.call("yan_b200_read_device_status", ctypes.byref(status), int(reset))
-    return status.value
+    if status.value != 0:
+        return status.value
+    for runtime in _jit_runtimes_used.values():
+        word = runtime.read_device_status(reset)
+        if word != 0:
+            return word
+    return 0

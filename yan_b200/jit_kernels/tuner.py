@@ -52,69 +52,85 @@ class JITTuner:
         except (OSError, ValueError):
             pass
 
+    # ---- the four steps of compile_and_tune ----
+
+    @staticmethod
+    def _build_candidates(name, keys, space, includes, arg_defs, template):
+        """One compiled Runtime per entry of the space (a build that fails raises)."""
+        built = []
+        for extra in space:
+            assert isinstance(extra, dict), "every entry of the tuning space is a dict of template keys"
+            merged = {**copy.deepcopy(keys), **extra}
+            built.append((build(name, arg_defs, generate(includes, arg_defs, cpp_format(template, merged))), extra))
+        return built
+
+    @staticmethod
+    def _is_legal(runtime: Runtime, args: tuple) -> int:
+        """Launches once; the kernel's own return code says whether the configuration can run (0 = yes)."""
+        return runtime(*args)
+
+    @staticmethod
+    def _time(runtime: Runtime, args: tuple, scrub: torch.Tensor, launches: int = 20) -> float:
+        """Milliseconds for `launches` back-to-back launches after the L2 has been overwritten."""
+        first, last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        scrub.zero_()
+        first.record()
+        for _ in range(launches):
+            code = runtime(*args)
+            assert code == 0, f"a launch that was legal a moment ago returned {code}"
+        last.record()
+        last.synchronize()
+        return first.elapsed_time(last)
+
     def compile_and_tune(self, name: str, keys: Dict[str, Any], space: tuple, includes: tuple, arg_defs: tuple,
                          template: str, args: tuple) -> Runtime:
-        # The space and the template are assumed not to change for a given (name, keys), and the
-        # kernel must have no accumulating side effect: it is launched repeatedly while timing.
-        keys = {k: keys[k] for k in sorted(keys.keys())}
-        signature = (name, f"{keys}")
-        if signature in self.tuned:
-            if os.getenv("YAN_JIT_DEBUG", None):
-                print(f"Using cached JIT kernel {name} with keys {keys}")
-            return self.tuned[signature]
-        if os.getenv("YAN_JIT_DEBUG", None):
-            print(f"Auto-tuning JIT kernel {name} with keys {keys}")
-        assert args is not None
-        space = (dict(),) if len(space) == 0 else space
+        """Signature and meaning of yan/jit_kernels/tuner.py:12: returns the fastest legal kernel of `space` for
+        (name, keys), remembered for the life of the process and, across processes, in tuned.json.
+        The space and the template must not change for a given (name, keys), and the kernel must be repeatable: it
+        is launched many times while it is timed."""
+        verbose = bool(os.getenv("YAN_JIT_DEBUG"))
+        keys = dict(sorted(keys.items()))
+        memo_key = (name, f"{keys}")
+        if memo_key in self.tuned:
+            if verbose:
+                print(f"[tuner] {name} {keys}: already tuned in this process")
+            return self.tuned[memo_key]
+        assert args is not None, "tuning needs one set of launch arguments"
+        candidates_space = tuple(space) if len(space) > 0 else ({},)
+        contest = len(candidates_space) > 1
 
         device = torch.cuda.get_device_name() if torch.cuda.is_available() else "nodevice"
         store_key = f"{name}|{keys}|{device}"
-        remembered = self._load_choice(store_key) if len(space) > 1 else None
-        if remembered is not None and remembered in list(space):
-            space = (remembered,)
+        if contest:
+            remembered = self._load_choice(store_key)
+            if remembered is not None and remembered in list(candidates_space):
+                if verbose:
+                    print(f"[tuner] {name} {keys}: tuned.json holds {remembered}")
+                candidates_space, contest = (remembered,), False
 
-        kernels = []
-        for tuned_keys in space:
-            assert isinstance(tuned_keys, dict)
-            full_keys = copy.deepcopy(keys)
-            full_keys.update(tuned_keys)
-            code = generate(includes, arg_defs, cpp_format(template, full_keys))
-            kernels.append((build(name, arg_defs, code), tuned_keys))  # an illegal build raises
-
-        best_runtime, best_time, best_keys = None, None, None
-        flush = None
-        for runtime, tuned_keys in kernels:
-            if len(space) > 1:
-                return_code = runtime(*args)
-                if return_code != 0:
-                    if os.getenv("YAN_JIT_DEBUG", None):
-                        print(f"Illegal JIT kernel {name} with keys {keys} and tuned keys {tuned_keys}: "
-                              f"error code {return_code}")
+        built = self._build_candidates(name, keys, candidates_space, includes, arg_defs, template)
+        if not contest:
+            winner, winner_keys, winner_ms = built[0][0], built[0][1], 0.0
+        else:
+            scrub = torch.empty(l2_flush_bytes() // 4, dtype=torch.int, device="cuda")
+            winner, winner_keys, winner_ms = None, None, None
+            for runtime, extra in built:
+                code = self._is_legal(runtime, args)
+                if code != 0:
+                    if verbose:
+                        print(f"[tuner] {name} {keys} + {extra}: refused with return code {code}, skipped")
                     continue
-                if flush is None:
-                    flush = torch.empty(l2_flush_bytes() // 4, dtype=torch.int, device="cuda")
-                start = torch.cuda.Event(enable_timing=True)
-                end = torch.cuda.Event(enable_timing=True)
-                flush.zero_()
-                start.record()
-                for _ in range(20):
-                    assert runtime(*args) == 0
-                end.record()
-                end.synchronize()
-                elapsed = start.elapsed_time(end)
-            else:
-                elapsed = 0
-            if best_time is None or elapsed < best_time:
-                best_runtime, best_time, best_keys = runtime, elapsed, tuned_keys
-            if os.getenv("YAN_JIT_DEBUG", None):
-                print(f"Tuned JIT kernel {name} with keys {keys} and tuned keys {tuned_keys} has time {elapsed}")
-        assert best_runtime is not None, f"Failed to tune JIT kernel {name} with keys {keys}"
-        if os.getenv("YAN_JIT_DEBUG", None) or os.getenv("YAN_PRINT_AUTOTUNE", None):
-            print(f"Best JIT kernel {name} with keys {keys} has tuned keys {best_keys} and time {best_time}")
-        if len(kernels) > 1:
-            self._save_choice(store_key, best_keys)
-        self.tuned[signature] = best_runtime
-        return best_runtime
+                ms = self._time(runtime, args, scrub)
+                if verbose:
+                    print(f"[tuner] {name} {keys} + {extra}: {ms:.3f} ms for 20 launches")
+                if winner_ms is None or ms < winner_ms:
+                    winner, winner_keys, winner_ms = runtime, extra, ms
+            assert winner is not None, f"no configuration of {name} with keys {keys} could be launched"
+            self._save_choice(store_key, winner_keys)
+        if verbose or os.getenv("YAN_PRINT_AUTOTUNE"):
+            print(f"[tuner] {name} {keys}: chose {winner_keys} ({winner_ms:.3f} ms)")
+        self.tuned[memo_key] = winner
+        return winner
 
 
 jit_tuner = JITTuner()

@@ -45,55 +45,68 @@ def l2_flush_bytes() -> int:
     return 2 * max(int(l2), 64 << 20)
 
 
+def _line_up_ranks() -> None:
+    """A large matmul and a one-element all-reduce: every rank reaches the profiled calls at about the same time."""
+    x = torch.randn((4096, 4096), dtype=torch.float, device="cuda")
+    torch.mm(x, x)
+    dist.all_reduce(torch.ones(1, dtype=torch.float, device="cuda"))
+
+
+def _kernel_seconds(events, wanted: str) -> float:
+    """Mean device time of the one profiled kernel whose name contains `wanted`."""
+    hits = [e for e in events if wanted in e.key]
+    if len(hits) != 1:
+        found = sorted(e.key for e in events)
+        raise AssertionError(f"'{wanted}' must name exactly one profiled kernel, it matches {len(hits)} of {found}")
+    event = hits[0]
+    total_us = getattr(event, "device_time_total", None)
+    if total_us is None:  # older profiler builds
+        total_us = event.cuda_time_total
+    return float(total_us) / max(int(event.count), 1) / 1e6
+
+
 def bench_kineto(fn, kernel_names, num_tests: int = 30, suppress_kineto_output: bool = False,
                  trace_path: str = None, barrier_comm_profiling: bool = False, flush_l2: bool = False):
-    """Average device time (seconds) of the kernels whose profiler row contains `kernel_names`
-    (a string or a tuple of strings; each must match exactly one row).  Same procedure as
-    yan/utils.py:50-107: one warm call, a torch.profiler pass over 2 x num_tests calls, optional L2
-    flush before each call, optional large matmul + all-reduce to line ranks up, table parsing."""
-    using_nsys = os.environ.get("YAN_NSYS_PROFILING", False)
+    """Mean device time in seconds of the kernel(s) named by `kernel_names` while `fn` runs under the profiler.
+
+    Keeps the contract of the reference's helper (yan/utils.py:50-107): `kernel_names` is a substring or a tuple of
+    substrings, each of which has to match exactly one profiled kernel; a tuple in gives a tuple out; `fn` is called
+    once to warm up and then 2 x `num_tests` times, of which the second batch is the one recorded;
+    `barrier_comm_profiling` lines the ranks up before each batch; `trace_path` writes a chrome trace;
+    YAN_NSYS_PROFILING=1 runs the calls without the profiler (for an outer tool) and returns 1.
+    Here the times come from the profiler's event records (name, total device time, count) and, with `flush_l2`,
+    a buffer of twice the L2 size is overwritten before every call."""
+    if not isinstance(kernel_names, (str, tuple)):
+        raise AssertionError("kernel_names is a string or a tuple of strings")
+    outer_tool = bool(os.environ.get("YAN_NSYS_PROFILING", False))
+    scrub = torch.empty(l2_flush_bytes() // 4, dtype=torch.int, device="cuda") if flush_l2 else None
+
+    def batch():
+        if barrier_comm_profiling:
+            _line_up_ranks()
+        for _ in range(num_tests):
+            if scrub is not None:
+                scrub.zero_()
+            fn()
+
     fn()
-    flush = torch.empty(l2_flush_bytes() // 4, dtype=torch.int, device="cuda") if flush_l2 else None
-    suppress = suppress_stdout_stderr if suppress_kineto_output and not using_nsys else empty_suppress
-    with suppress():
-        schedule = torch.profiler.schedule(wait=0, warmup=1, active=1, repeat=1) if not using_nsys else None
-        profiler = (torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CUDA], schedule=schedule)
-                    if not using_nsys else empty_suppress())
-        with profiler:
-            for _ in range(2):
-                if barrier_comm_profiling:
-                    lhs = torch.randn((4096, 4096), dtype=torch.float, device="cuda")
-                    rhs = torch.randn((4096, 4096), dtype=torch.float, device="cuda")
-                    lhs @ rhs
-                    dist.all_reduce(torch.ones(1, dtype=torch.float, device="cuda"))
-                for _ in range(num_tests):
-                    if flush is not None:
-                        flush.zero_()
-                    fn()
-                if not using_nsys:
-                    profiler.step()
-    if using_nsys:
+    if outer_tool:
+        batch()
+        batch()
         return 1
-    assert isinstance(kernel_names, (str, tuple))
-    is_tupled = isinstance(kernel_names, tuple)
-    lines = profiler.key_averages().table(sort_by="cuda_time_total", max_name_column_width=300).split("\n")
-    names = (kernel_names,) if isinstance(kernel_names, str) else kernel_names
-    for name in names:
-        assert sum(name in line for line in lines) == 1, f"Errors of the kernel {name} in the profiling table: {lines}"
+    quiet = suppress_stdout_stderr if suppress_kineto_output else empty_suppress
+    with quiet():
+        plan = torch.profiler.schedule(wait=0, warmup=1, active=1, repeat=1)
+        with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CUDA], schedule=plan) as prof:
+            for _ in range(2):
+                batch()
+                prof.step()
     if trace_path is not None:
-        profiler.export_chrome_trace(trace_path)
-    units = {"ms": 1e3, "us": 1e6}
-    times = []
-    for name in names:
-        for line in lines:
-            if name in line:
-                t = line.split()[-2]
-                for unit, scale in units.items():
-                    if unit in t:
-                        times.append(float(t.replace(unit, "")) / scale)
-                        break
-                break
-    return tuple(times) if is_tupled else times[0]
+        prof.export_chrome_trace(trace_path)
+    events = list(prof.key_averages())
+    if isinstance(kernel_names, str):
+        return _kernel_seconds(events, kernel_names)
+    return tuple(_kernel_seconds(events, name) for name in kernel_names)
 
 
 def bench_events(fn, num_tests: int = 20, warmup: int = 3, flush_l2: bool = True) -> float:
@@ -116,18 +129,12 @@ def bench_events(fn, num_tests: int = 20, warmup: int = 3, flush_l2: bool = True
 
 
 def calc_diff(x: torch.Tensor, y: torch.Tensor):
-    """1 - 2<x,y>/(|x|^2 + |y|^2)  (yan/utils.py:109-113)."""
-    x, y = x.double(), y.double()
-    denominator = (x * x + y * y).sum()
-    sim = 2 * (x * y).sum() / denominator
-    return 1 - sim
+    """Dissimilarity 1 - 2<x,y> / (|x|^2 + |y|^2) in float64: 0 for equal tensors, the reference's acceptance
+    metric (`< 1e-3`, yan/utils.py:109-113)."""
+    xd, yd = x.double().flatten(), y.double().flatten()
+    return 1 - 2 * torch.dot(xd, yd) / (torch.dot(xd, xd) + torch.dot(yd, yd))
 
 
 def count_bytes(tensors) -> int:
-    total = 0
-    for t in tensors:
-        if isinstance(t, tuple):
-            total += count_bytes(t)
-        else:
-            total += t.numel() * t.element_size()
-    return total
+    """Bytes held by a (possibly nested) tuple of tensors."""
+    return sum(count_bytes(t) if isinstance(t, tuple) else t.numel() * t.element_size() for t in tensors)
