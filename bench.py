@@ -565,6 +565,11 @@ def run_reference(args) -> None:
 
 
 def run_ours(args) -> None:
+    # Libraries may write to stdout (NCCL prints its version there): keep the real stdout for the one JSON line and send
+    # everything else written to descriptor 1 to stderr.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     import yan_b200
     peaks = load_peaks()
     rank, world, local, dist = dist_setup(args.gpus)
@@ -735,7 +740,9 @@ def run_ours(args) -> None:
                                 "sample": f"{reps} passes over a {CPU_SLAB_ROWS}-row slab of A against the full B "
                                           f"(quantize, dequantize both operands, fp32 torch.matmul, bf16)"}
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        sys.stdout.flush()
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
+    os.close(json_fd)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
