@@ -511,6 +511,17 @@ def multi_gpu_parity(rank: int, world: int, dist) -> dict:
             comm.close()
     except Exception as e:
         out["peer_memory"] = {"unavailable": f"{type(e).__name__}: {e}"[:160]}
+    # the host front end with sharded input: the gathered operand must equal the quantizer's output on all of A
+    pipe = yan_b200.HostFp8Linear(rhs_n, m, depth=1, shard_input=True)
+    a_pinned = a.contiguous().pin_memory()
+    d_pinned = torch.empty(m, n // world, dtype=torch.bfloat16).pin_memory()
+    pipe.submit(a_pinned, d_pinned)
+    pipe.wait()
+    q_all, s_all = yan_b200.per_token_cast_to_fp8(a.cuda())
+    same = bool(torch.equal(pipe.lhs[0][0].view(torch.uint8), q_all.view(torch.uint8)) and torch.equal(pipe.lhs[0][1], s_all))
+    record("host_front_end_sharded_input", d_pinned, d_ref[:, rank * (n // world):(rank + 1) * (n // world)], 1e-3,
+           {"gathered_operand_bit_exact_vs_local_quantizer": same})
+    del pipe
     status = torch.tensor([float(yan_b200.read_device_status())], device="cuda", dtype=torch.float64)
     dist.all_reduce(status, op=dist.ReduceOp.MAX)
     out["device_status"] = int(status.item())
@@ -638,7 +649,8 @@ def run_ours(args) -> None:
     # host front end (three streams, two rotating device slots: copies of one step overlap kernels of the next) ----
     a_host = a.cpu().pin_memory()
     out_hosts = [torch.empty(M, n_local, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
-    pipe = yan_b200.HostFp8Linear(rhs, M, depth=2)
+    # several ranks: each pulls only its share of A's rows over its host link and the ranks all-gather the quantized rows
+    pipe = yan_b200.HostFp8Linear(rhs, M, depth=2, shard_input=(world > 1))
     e2e_steps = max(4, min(args.steps, 10))
     for i in range(2):
         pipe.submit(a_host, out_hosts[i % 2])
@@ -657,14 +669,18 @@ def run_ours(args) -> None:
     a_dev = torch.empty_like(a)
     torch.cuda.synchronize()
     s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    serial = yan_b200.HostFp8Linear(rhs, M, depth=1, shard_input=(world > 1))
+    serial.submit(a_host, out_hosts[0])
+    serial.wait()
+    barrier()
     s0.record()
-    a_dev.copy_(a_host, non_blocking=True)
-    yan_b200.per_token_cast_to_fp8(a_dev, out=lhs)
-    yan_b200.gemm_fp8_fp8_bf16_nt(lhs, rhs, out)
-    out_hosts[0].copy_(out, non_blocking=True)
+    serial.submit(a_host, out_hosts[0])
+    torch.cuda.current_stream().wait_stream(serial.copy_out)
     s1.record()
-    torch.cuda.synchronize()
+    serial.wait()
     e2e_serial_ms = s0.elapsed_time(s1)
+    h2d_bytes = pipe.h2d_bytes_per_call()
+    del serial
     if dist is not None:
         t = torch.tensor([e2e_ms, e2e_serial_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -694,11 +710,14 @@ def run_ours(args) -> None:
             "vs_baseline": None, "dtype": "e4m3 (fp32 accumulate, bf16 out)", "data": "synthetic",
             "config": workload_config(world), "device": dev_name,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": a_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
+                    "h2d_bytes_per_step": h2d_bytes * world, "d2h_bytes_per_step": out_host.numel() * 2 * world,
+                    "h2d_bytes_per_step_per_gpu": h2d_bytes, "d2h_bytes_per_step_per_gpu": out_host.numel() * 2,
                     "single_step_latency_ms": e2e_serial_ms,
                     "note": "yan_b200.HostFp8Linear: weights resident on the device; every step copies A in from pinned "
                             "host memory and D out to pinned host memory; copies of one step overlap the kernels of the "
-                            "next (2 device slots, 3 streams)"},
+                            "next (2 device slots, 3 streams)" +
+                            ("; every rank copies and quantizes M/g rows of A and the ranks all-gather the e4m3 codes and "
+                             "scales over NVLink (bit-identical to quantizing all of A on every rank)" if world > 1 else "")},
             "gpu_launches": 2 * args.steps, "clocks": clocks, "roofline": roofline}
     if parity is not None:
         line["parity"] = parity
