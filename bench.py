@@ -349,6 +349,38 @@ def bench_sustained(step, flops_per_step: float, burst_ms: float, device_index: 
             "clock_samples": clocks.get("samples_in_timed_region"), "reasons": clocks.get("reasons")}
 
 
+def bench_reference_blackwell_gemm(peaks, m: int = 8192, n: int = 8192, k: int = 8192) -> dict:
+    """Same-GPU yardstick: the reference's own Blackwell program (comm/gemm.cu: CUTLASS fp16 GEMM, its own timing loop)
+    run as a separate process on M=N=K=8192, beside this package's FP8 GEMM on the same M, N, K.  One GPU only."""
+    import yan_b200
+    from yan_b200.utils import bench_events
+    a, rhs = make_device_inputs(m, n, k, 0)
+    lhs = yan_b200.per_token_cast_to_fp8(a)
+    out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    t = bench_events(lambda: yan_b200.gemm_fp8_fp8_bf16_nt(lhs, rhs, out), num_tests=10, flush_l2=True)
+    ours = 2.0 * m * n * k / t / 1e12
+    del a, rhs, lhs, out
+    torch.cuda.empty_cache()
+    res = {"workload": f"same-GPU yardstick M={m} N={n} K={k}", "fp8_gemm_TFLOP/s (this package)": ours,
+           "fp8_gemm_us": t * 1e6}
+    binary = os.path.join(ROOT, "oracle", "_ref", "ref_gemm_sm100")
+    if not os.path.exists(binary):
+        res["reference_fp16_gemm"] = "unavailable: oracle/_ref/ref_gemm_sm100 was not built (needs the reference tree and CUTLASS headers)"
+        return res
+    try:
+        r = subprocess.run([binary, f"--m={m}", f"--n={n}", f"--k={k}", "--iterations=10"], capture_output=True, text=True,
+                           timeout=180)
+        gflops = [float(line.split(":")[1]) for line in r.stdout.splitlines() if line.strip().startswith("GFLOPS")]
+        if r.returncode != 0 or not gflops:
+            res["reference_fp16_gemm"] = f"unavailable: exit code {r.returncode}: {(r.stdout + r.stderr)[-200:]}"
+            return res
+        res["reference_fp16_gemm_TFLOP/s (comm/gemm.cu, CUTLASS 256x128x64, cluster 2x2)"] = gflops[0] / 1e3
+        res["fp8_over_reference_fp16"] = ours / (gflops[0] / 1e3)
+    except Exception as e:
+        res["reference_fp16_gemm"] = f"unavailable: {type(e).__name__}: {e}"[:200]
+    return res
+
+
 def _time_k_split(step, dist, steps: int, m: int, n: int, k: int, flops: bool = True) -> dict:
     for _ in range(3):
         step()
@@ -743,9 +775,13 @@ def run_ours(args) -> None:
         extras.append(bench_fused_epilogue(8192, 7168, 2048, peaks=peaks))
         extras.append(bench_fused_epilogue(M, N, K, iters=5, peaks=peaks))
         extras.append(bench_grouped(peaks))
+        extras.append(bench_reference_blackwell_gemm(peaks))
         if sustained is not None:
             extras.append(sustained)
         line["other_workloads"] = extras
+        from yan_b200.utils import perf_log
+        for record in extras:  # one JSON line per side measurement when YAN_PERF_LOG names a file
+            perf_log(record)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         a_cpu, rhs_cpu = make_cpu_inputs()
         cpu_reference_step(a_cpu, rhs_cpu)

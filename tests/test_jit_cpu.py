@@ -117,3 +117,15 @@ def test_host_utils():
     assert utils.get_col_major_tensor(c).data_ptr() == c.data_ptr()  # already column-major: no copy
     from yan_b200 import utils as U
     assert abs(float(U.calc_diff(x, x))) < 1e-12 and U.count_bytes((x, (x, x))) == 3 * 48
+
+
+def test_perf_log_appends_json_lines(tmp_path, monkeypatch):
+    import json
+    from yan_b200.utils import perf_log
+    path = tmp_path / "perf.jsonl"
+    perf_log({"workload": "ignored: no file named"})
+    monkeypatch.setenv("YAN_PERF_LOG", str(path))
+    perf_log({"workload": "C1", "us": 10.5, "TFLOP/s": 51.0})
+    perf_log({"workload": "C2", "us": 5.4, "GB/s": 2750.0})
+    lines = [json.loads(line) for line in path.read_text().splitlines()]
+    assert [r["workload"] for r in lines] == ["C1", "C2"] and lines[0]["us"] == 10.5 and "unix_time" in lines[1]

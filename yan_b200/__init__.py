@@ -14,6 +14,6 @@ from .jit_kernels import (ceil_div, fp8_linear, fp8_linear_workspace_bytes, gemm
                           per_block_cast_to_fp8, per_token_cast_to_fp8, read_device_status, set_num_sms,
                           set_programmatic_dependent_launch, set_clock_probe, effective_sm_clock_mhz, set_split_k)
 from .jit_kernels import HostFp8Linear
-from .utils import bench_events, bench_kineto, calc_diff, count_bytes
+from .utils import bench_events, bench_kineto, calc_diff, count_bytes, perf_log
 
 __version__ = "0.1.0"

@@ -128,6 +128,23 @@ def bench_events(fn, num_tests: int = 20, warmup: int = 3, flush_l2: bool = True
     return sum(s.elapsed_time(e) for s, e in zip(starts, ends)) / num_tests / 1e3
 
 
+def perf_log(record: dict, path: str = None) -> None:
+    """Appends one JSON line (shape, configuration, microseconds, TFLOP/s or GB/s, roofline fraction, error figures:
+    whatever the caller measured) to the file named by `path` or by the YAN_PERF_LOG environment variable; a no-op
+    when neither is set.  Tables of measurements are generated from this log rather than copied by hand."""
+    import json
+    import time
+    path = path or os.environ.get("YAN_PERF_LOG")
+    if not path:
+        return
+    line = dict(record)
+    line.setdefault("unix_time", round(time.time(), 3))
+    if torch.cuda.is_available():
+        line.setdefault("device", torch.cuda.get_device_name())
+    with open(path, "a") as f:
+        f.write(json.dumps(line, sort_keys=True) + "\n")
+
+
 def calc_diff(x: torch.Tensor, y: torch.Tensor):
     """Dissimilarity 1 - 2<x,y> / (|x|^2 + |y|^2) in float64: 0 for equal tensors, the reference's acceptance
     metric (`< 1e-3`, yan/utils.py:109-113)."""
