@@ -61,23 +61,6 @@ void yan_b200_gemm_fp8_fp8_bf16_nt(const void* lhs, const void* lhs_scales, cons
                                    void* out, int m, int n, int k, int ldd, void* stream, int num_sms, int block_n,
                                    int* return_code);
 
-/*
- * The same GEMM, allowed to cut tiles along K.  When the tile count is a little more than a multiple of the grid, the
- * last wave of whole tiles leaves most SMs idle (896 tiles on 148 SMs run as 7 waves for 6.05 waves of work); with a
- * workspace the k-blocks of the last (grid + remainder) tiles are dealt out evenly instead, a tile that straddles two
- * CTAs being summed through the workspace (fp32 partials, the CTA that finishes second adds and stores; nobody waits).
- * The result can differ from yan_b200_gemm_fp8_fp8_bf16_nt in the last bit of an element (two partial sums are added
- * instead of one running sum); it meets the same tolerance against the dequantize-and-matmul result.
- * workspace: device memory, 256-byte aligned, at least yan_b200_gemm_split_workspace_bytes(num_sms) bytes, whose first
- * 1024 bytes are zero before the first call (every call leaves them zero); NULL = never cut.  Two launches that may run
- * at the same time need a workspace each.  Follows the persistent scheduler the reference sketches
- * (yan/include/gemm/scheduler.cuh:20,39-41), which only knows whole tiles.
- */
-size_t yan_b200_gemm_split_workspace_bytes(int num_sms);
-void yan_b200_gemm_fp8_fp8_bf16_nt_split(const void* lhs, const void* lhs_scales, const void* rhs, const void* rhs_scales,
-                                         void* out, int m, int n, int k, int ldd, void* stream, int num_sms, int block_n,
-                                         void* workspace, size_t workspace_bytes, int* return_code);
-
 /* Same GEMM with the next layer's quantizer fused into the epilogue: out = e4m3 [M, ldd] (ldd % 16 == 0, 16-byte
  * aligned) and out_scales = fp32, k-block-major [N/128][out_scales_ld] (out_scales_ld >= m), i.e. exactly what
  * yan_b200_per_token_cast_to_fp8 would produce from the bf16 output of yan_b200_gemm_fp8_fp8_bf16_nt (the accumulator is

@@ -48,11 +48,6 @@ struct GemmParams {
     uint32_t shape_n;
     uint32_t shape_k;
     uint32_t num_groups;
-    // split-K of the tail of the tile space (Normal kind, see Scheduler): 0 tiles = off.  `split_counters` holds one
-    // zeroed word per CTA boundary (left zero by the kernel), `split_partials` two fp32 tiles of 128 x BLOCK_N per boundary.
-    uint32_t split_tiles = 0;
-    unsigned int* split_counters = nullptr;
-    float* split_partials = nullptr;
     int* status;  // optional device word: 0 = fine, otherwise (kDeviceTimeout << 8) | site
     unsigned long long timeout_ns;
     // optional: CTA 0 writes {clock64, globaltimer} when it starts and when it ends (4 values), so that the host can
@@ -174,12 +169,11 @@ struct GemmSmemLayout {
         (kOffStore + kNumStoreBoxes * kStoreBoxBytes + 2048 <= 232448) ? kNumStoreBoxes * kStoreBoxBytes : 0;
     static constexpr uint32_t kOffBarriers = kOffStore + kStoreBytes;
     // ring full/empty, TMEM full/empty per buffer and column half
-    static constexpr uint32_t kNumBarriers = 2 * kNumStages + 4 * kNumTmemBufs + 1;  // + the promotion warps' own barrier
+    static constexpr uint32_t kNumBarriers = 2 * kNumStages + 4 * kNumTmemBufs;
     static constexpr uint32_t kOffTmemSlot = kOffBarriers + kNumBarriers * 8;
     static constexpr uint32_t kOffAbort = kOffTmemSlot + 4;
-    static constexpr uint32_t kOffSeamFlag = kOffAbort + 4;
     // +1024: the dynamic shared-memory base is re-aligned to 1024 bytes inside the kernel.
-    static constexpr uint32_t kSmemSize = kOffSeamFlag + 4 + 1024;
+    static constexpr uint32_t kSmemSize = kOffAbort + 4 + 1024;
     static_assert(kTmemColsUsed <= 512, "tensor memory has 512 columns");
     static_assert(BLOCK_N % 32 == 0 && BLOCK_N >= 32 && BLOCK_N <= 256, "UMMA M=128 needs N % 16 == 0, N <= 256");
 };
@@ -269,7 +263,6 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     uint64_t* empty_barriers = full_barriers + kNumStages;
     uint64_t* tmem_full_barriers = empty_barriers + kNumStages;            // [buf][half]
     uint64_t* tmem_empty_barriers = tmem_full_barriers + 2 * kNumTmemBufs;  // [buf][half]
-    uint64_t* promo_barrier = tmem_empty_barriers + 2 * kNumTmemBufs;        // all promotion warps (split-K seams)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kOffTmemSlot);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kOffAbort);
 
@@ -293,7 +286,6 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
             ptx::mbar_init(tmem_full_barriers + i, 1);                             // tcgen05.commit
             ptx::mbar_init(tmem_empty_barriers + i, kNumMathWarps / kNumHalves);  // one arrival per promotion warp
         }
-        ptx::mbar_init(promo_barrier, kNumMathWarps);
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::fence_proxy_async_smem();
@@ -317,18 +309,15 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
         if (warp_idx == 0 && lane_idx == 0) {
             // ------------------------------ TMA producer ------------------------------
             Sched sched(p.shape_m, p.shape_n, p.grouped_layout, p.num_groups);
-            sched.set_k_range(num_k_blocks, p.split_tiles);
-            WorkItem item;
-            uint32_t stage = 0, phase = 0;
+            uint32_t m_block_idx, n_block_idx, stage = 0, phase = 0;
             bool alive = true;
             [[maybe_unused]] long long waited_empty = 0;
-            while (alive && sched.get_next_item(item)) {
-                const uint32_t m_block_idx = item.m_block_idx, n_block_idx = item.n_block_idx;
+            while (alive && sched.get_next_block(m_block_idx, n_block_idx)) {
                 const int group = sched.get_group(m_block_idx);
                 if (group < 0) continue;
                 const int32_t a_row = static_cast<int32_t>(sched.get_row_base(m_block_idx));
                 const int32_t b_row = static_cast<int32_t>(group * p.shape_n + n_block_idx * BLOCK_N);
-                for (uint32_t kb = item.kb_begin; kb < item.kb_end; ++kb) {
+                for (uint32_t kb = 0; kb < num_k_blocks; ++kb) {
                     YAN_STAMP(w0);
                     if (!detail::bounded_wait(empty_barriers + stage, phase ^ 1, abort_flag, p, 1)) {
                         alive = false;
@@ -364,15 +353,13 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
             // rows [kUmmaN, BLOCK_N) of the B tile start kUmmaN 128-byte rows further on (whole 8-row swizzle atoms)
             constexpr uint32_t kDescHalfStep = (kUmmaN * kBlockK) >> 4;
             static_assert(kUmmaN % 16 == 0, "UMMA with M = 128 needs N % 16 == 0");
-            sched.set_k_range(num_k_blocks, p.split_tiles);
-            WorkItem item;
-            uint32_t stage = 0, phase = 0, buf = 0, buf_phase = 0;
+            uint32_t m_block_idx, n_block_idx, stage = 0, phase = 0, buf = 0, buf_phase = 0;
             bool alive = true;
             [[maybe_unused]] long long waited_full = 0, waited_tmem = 0;
             YAN_STAMP(mma_begin);
-            while (alive && sched.get_next_item(item)) {
-                if (sched.get_group(item.m_block_idx) < 0) continue;
-                for (uint32_t kb = item.kb_begin; kb < item.kb_end && alive; ++kb) {
+            while (alive && sched.get_next_block(m_block_idx, n_block_idx)) {
+                if (sched.get_group(m_block_idx) < 0) continue;
+                for (uint32_t kb = 0; kb < num_k_blocks && alive; ++kb) {
                     YAN_STAMP(w0);
                     if (!detail::bounded_wait(full_barriers + stage, phase, abort_flag, p, 2)) {
                         alive = false;
@@ -434,65 +421,47 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
         const uint32_t half = kSplitHalves ? wg : 0;
 
         Sched sched(p.shape_m, p.shape_n, p.grouped_layout, p.num_groups);
-        sched.set_k_range(num_k_blocks, p.split_tiles);
-        WorkItem item;
-        uint32_t buf = 0, buf_phase = 0, promo_phase = 0;
+        uint32_t m_block_idx, n_block_idx, buf = 0, buf_phase = 0;
         bool alive = true, next_ready = false;
-        // Barrier over the promotion warps with the same bounded wait as everything else (a named hardware barrier
-        // cannot give up): false when it ran out or another role aborted.
-        auto promo_sync = [&]() -> bool {
-            __syncwarp();
-            if (lane_idx == 0) ptx::mbar_arrive(promo_barrier);
-            const bool ok = detail::bounded_wait(promo_barrier, promo_phase, abort_flag, p, 6);
-            promo_phase ^= 1;
-            return __all_sync(0xffffffffu, ok);
-        };
         float acc[kColsPerWG];
         [[maybe_unused]] long long waited_tmem_full = 0, in_loads = 0, in_fmas = 0, in_stores = 0, promoted = 0;
         YAN_STAMP(promo_begin);
 
-        while (alive && sched.get_next_item(item)) {
-            const uint32_t m_block_idx = item.m_block_idx, n_block_idx = item.n_block_idx;
-            const uint32_t kb_first = item.kb_begin, kb_last = item.kb_end;
+        while (alive && sched.get_next_block(m_block_idx, n_block_idx)) {
             const int group = sched.get_group(m_block_idx);
             if (group < 0) continue;
             const uint32_t row = sched.get_row_base(m_block_idx) + row_in_tile;
             const bool row_ok = row < sched.get_row_limit();
             const uint32_t n_first = n_block_idx * BLOCK_N + col0;
             const uint32_t sb_row = min(n_first / 128u, num_sb_rows - 1);
-            // scale pointers of this item's first k-block
-            const float* sa_ptr = p.scales_a + static_cast<size_t>(kb_first) * p.sa_ld + row;
-            const float* sb_ptr =
-                p.scales_b + (static_cast<size_t>(group) * num_sb_rows + sb_row) * num_k_blocks + kb_first;
+            const float* sa_ptr = p.scales_a + row;
+            const float* sb_ptr = p.scales_b + (static_cast<size_t>(group) * num_sb_rows + sb_row) * num_k_blocks;
             const float* sa_next = sa_ptr + static_cast<size_t>(kScaleDepth) * p.sa_ld;  // row's scale kScaleDepth k-blocks ahead
             // two-scale case: groups of 16 columns from `hi_from` on belong to the next 128-column block
             const uint32_t hi_from = kTwoScales ? (128u - n_first % 128u) / 16u : 0xFFFFu;
-            const float* sb_hi_ptr = p.scales_b +
-                                     (static_cast<size_t>(group) * num_sb_rows + min(sb_row + 1, num_sb_rows - 1)) * num_k_blocks +
-                                     kb_first;
-            const uint32_t item_k_blocks = kb_last - kb_first;
+            const float* sb_hi_ptr =
+                p.scales_b + (static_cast<size_t>(group) * num_sb_rows + min(sb_row + 1, num_sb_rows - 1)) * num_k_blocks;
 
             // Scales are prefetched kScaleDepth k-blocks ahead: one L2 round trip is longer than one k-block.
             float sa_ring[kScaleDepth], sb_ring[kScaleDepth], sb_hi_ring[kTwoScales ? kScaleDepth : 1];
 #pragma unroll
             for (uint32_t i = 0; i < kScaleDepth; ++i) {
-                sa_ring[i] = (row_ok && i < item_k_blocks) ? __ldg(sa_ptr + static_cast<size_t>(i) * p.sa_ld) : 0.0f;
-                sb_ring[i] = (i < item_k_blocks) ? __ldg(sb_ptr + i) : 0.0f;
-                if constexpr (kTwoScales) sb_hi_ring[i] = (i < item_k_blocks) ? __ldg(sb_hi_ptr + i) : 0.0f;
+                sa_ring[i] = (row_ok && i < num_k_blocks) ? __ldg(sa_ptr + static_cast<size_t>(i) * p.sa_ld) : 0.0f;
+                sb_ring[i] = (i < num_k_blocks) ? __ldg(sb_ptr + i) : 0.0f;
+                if constexpr (kTwoScales) sb_hi_ring[i] = (i < num_k_blocks) ? __ldg(sb_hi_ptr + i) : 0.0f;
             }
 #pragma unroll
             for (uint32_t j = 0; j < kColsPerWG; ++j) acc[j] = 0.0f;
 
-            // kb counts from the item's first k-block
-            for (uint32_t kb0 = 0; kb0 < item_k_blocks && alive; kb0 += kScaleDepth) {
+            for (uint32_t kb0 = 0; kb0 < num_k_blocks && alive; kb0 += kScaleDepth) {
 #pragma unroll
                 for (uint32_t i = 0; i < kScaleDepth; ++i) {
                     const uint32_t kb = kb0 + i;
-                    if (!alive || kb >= item_k_blocks) continue;
+                    if (!alive || kb >= num_k_blocks) continue;
                     const float scale = sa_ring[i] * sb_ring[i];
                     float scale_hi = scale;
                     if constexpr (kTwoScales) scale_hi = sa_ring[i] * sb_hi_ring[i];
-                    if (kb + kScaleDepth < item_k_blocks) {
+                    if (kb + kScaleDepth < num_k_blocks) {
                         sa_ring[i] = row_ok ? __ldg(sa_next) : 0.0f;
                         sa_next += p.sa_ld;
                         sb_ring[i] = __ldg(sb_ptr + kb + kScaleDepth);
@@ -562,34 +531,7 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
                 }
             }
             YAN_STAMP(s0);
-            bool store_tile = alive;
-            if (alive && item.seam >= 0) {
-                // This CTA holds one side of a tile that is cut along K.  Both sides write their fp32 partial into the
-                // seam's slot (column-major: 32 lanes = 32 consecutive rows = one 128-byte line per store), then count
-                // themselves; the side that counts last adds the other side's partial to its registers and stores the
-                // tile.  Nobody waits for anybody.  (A sum of two fp32 terms does not depend on who adds.)
-                float* mine = p.split_partials + (static_cast<size_t>(item.seam) * 2 + item.part) * (kBlockM * BLOCK_N) +
-                              col0 * kBlockM + row_in_tile;
-                const float* theirs = p.split_partials +
-                                      (static_cast<size_t>(item.seam) * 2 + (item.part ^ 1u)) * (kBlockM * BLOCK_N) +
-                                      col0 * kBlockM + row_in_tile;
-#pragma unroll
-                for (uint32_t j = 0; j < kColsPerWG; ++j) mine[j * kBlockM] = acc[j];
-                __threadfence();
-                volatile uint32_t* seam_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kOffSeamFlag);
-                alive = promo_sync();  // every warp's partial is written
-                if (alive && warp_idx == 4 && lane_idx == 0) *seam_flag = atomicAdd(p.split_counters + item.seam, 1u);
-                alive = alive && promo_sync();
-                store_tile = alive && (*seam_flag == 1u);
-                if (store_tile) {
-                    __threadfence();
-#pragma unroll
-                    for (uint32_t j = 0; j < kColsPerWG; ++j) acc[j] += __ldcg(theirs + j * kBlockM);
-                }
-                alive = alive && promo_sync();  // everyone has read the flag before the next seam reuses it
-                if (store_tile && warp_idx == 4 && lane_idx == 0) p.split_counters[item.seam] = 0u;  // zero for the next launch
-            }
-            if (store_tile && row_ok) {
+            if (alive && row_ok) {
                 if constexpr (sizeof(out_t) == 1 && kColsPerWG != 128) {
                     // the e4m3 output needs one 128-column group per thread (BLOCK_N = 256, two warpgroups): the launcher
                     // refuses every other shape of CTA
@@ -604,7 +546,7 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
                 }
             }
             if constexpr (kStagedStore) {
-                if (store_tile) {
+                if (alive) {
                     // Lane r fills row r (64 bytes) of the warp's box; 16-byte chunk j of a row sits at chunk
                     // j ^ ((r / 2) % 4), which keeps both the row-wise writes and the read-back free of bank conflicts.
                     const uint32_t box = ptx::smem_u32(smem + L::kOffStore + (warp_idx - 4) * L::kStoreBoxBytes);
@@ -696,26 +638,7 @@ struct GemmArgs {
     int* status = nullptr;
     unsigned long long timeout_ns = 2000000000ull;
     long long* clock_probe = nullptr;  // optional: 4 values written by CTA 0 (see GemmParams)
-    // optional scratch for cutting the tail of the tile space along K (see split_k_workspace_bytes); the first
-    // kSplitCounterBytes bytes must be zero before the first launch that uses it and are left zero by every launch
-    void* split_workspace = nullptr;
-    size_t split_workspace_bytes = 0;
 };
-
-constexpr size_t kSplitCounterBytes = 1024;
-
-// Bytes of split-K scratch a grid of `num_sms` CTAs can use with BLOCK_N-wide tiles.
-constexpr size_t split_k_workspace_bytes(uint32_t num_sms, uint32_t block_n) {
-    return kSplitCounterBytes + (num_sms > 1 ? static_cast<size_t>(num_sms - 1) : 0) * 2 * kBlockM * block_n * sizeof(float);
-}
-
-// Tiles to cut along K: 0 unless a last, mostly empty wave would cost at least 3 % of the launch.
-inline uint32_t choose_split_tiles(uint32_t tiles, uint32_t grid, uint32_t num_k_blocks) {
-    if (grid < 2 || tiles <= grid || tiles % grid == 0 || num_k_blocks < 8) return 0;
-    const uint32_t waves = ceil_div(tiles, grid);
-    const double wasted = 1.0 - static_cast<double>(tiles) / (static_cast<double>(waves) * grid);
-    return wasted >= 0.03 ? grid + tiles % grid : 0;
-}
 
 inline bool is_aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
@@ -787,12 +710,6 @@ struct GemmLauncher {
         if (kGemmType != GemmType::GroupedMasked) {
             const uint32_t tiles = ceil_div(a.m, kBlockM) * ceil_div(a.n, BLOCK_N);
             grid = tiles < grid ? tiles : grid;
-            if (kGemmType == GemmType::Normal && a.split_workspace != nullptr && grid <= kSplitCounterBytes / 4 &&
-                is_aligned(a.split_workspace, 16) && a.split_workspace_bytes >= split_k_workspace_bytes(grid, BLOCK_N)) {
-                p.split_tiles = choose_split_tiles(tiles, grid, a.k / kBlockK);
-                p.split_counters = static_cast<unsigned int*>(a.split_workspace);
-                p.split_partials = reinterpret_cast<float*>(static_cast<uint8_t*>(a.split_workspace) + kSplitCounterBytes);
-            }
         }
         kernel<<<grid, get_num_threads_per_sm<>(BLOCK_N), kSmemSize, stream>>>(p, map_a, map_b);
         return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;

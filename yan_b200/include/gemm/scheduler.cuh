@@ -16,16 +16,6 @@ enum class GemmType {
     GroupedMasked       // A is [G,M_max,K], B is [G,N,K]; grouped_layout[g] = valid rows of group g
 };
 
-// One unit of work of a CTA: the k-blocks [kb_begin, kb_end) of one output tile.  A whole tile has seam < 0.  When the
-// tail of the tile space is split along K (see Scheduler::split_tiles), a tile cut at a CTA boundary is computed by two
-// CTAs: `seam` numbers the boundary (the workspace slot the two partial sums meet in) and `part` says which side
-// this CTA holds (0 = the tile's first k-blocks, 1 = its last).
-struct WorkItem {
-    uint32_t m_block_idx, n_block_idx, kb_begin, kb_end;
-    int seam;
-    uint32_t part;
-};
-
 template <GemmType kGemmType, uint32_t BLOCK_M, uint32_t BLOCK_N, uint32_t kNum1DBlocksPerGroup = 16>
 struct Scheduler {
     int current_iter = -1;
@@ -38,13 +28,6 @@ struct Scheduler {
     const int* grouped_layout;
     // GroupedMasked walk state
     uint32_t curr_group_idx = 0, curr_cumsum = 0;
-    // Split-K over the first `split_tiles` tiles (Normal kind only; 0 = every tile is computed whole by one CTA).
-    // With T tiles on G CTAs and T mod G small, the last wave would leave most SMs idle.  Instead the k-blocks of the
-    // first split_tiles = G + T mod G tiles form one run of split_tiles * num_k_blocks units that is cut into G equal
-    // contiguous shares (each at least one tile long, so a tile meets at most two CTAs and a CTA at most two cut
-    // tiles); the remaining tiles, a multiple of G, are computed whole, wave by wave.
-    uint32_t num_k_blocks = 0, split_tiles = 0;
-    uint32_t split_pos = 0, split_end = 0;
 
     __device__ __forceinline__ Scheduler(uint32_t shape_m_, uint32_t shape_n_, const int* grouped_layout_ = nullptr,
                                          uint32_t num_groups_ = 1)
@@ -52,50 +35,6 @@ struct Scheduler {
         num_m_blocks = ceil_div(shape_m, BLOCK_M);
         num_n_blocks = ceil_div(shape_n, BLOCK_N);
         num_blocks = num_m_blocks * num_n_blocks;
-    }
-
-    __device__ __forceinline__ void set_k_range(uint32_t num_k_blocks_, uint32_t split_tiles_) {
-        num_k_blocks = num_k_blocks_;
-        split_tiles = (kGemmType == GemmType::Normal) ? split_tiles_ : 0u;
-        if (split_tiles != 0) {
-            const uint32_t units = split_tiles * num_k_blocks, share = units / gridDim.x, extra = units % gridDim.x;
-            split_pos = blockIdx.x * share + min(blockIdx.x, extra);
-            split_end = split_pos + share + (blockIdx.x < extra ? 1u : 0u);
-        }
-    }
-
-    // Next unit of work of this CTA, false when there is none left.
-    __device__ __forceinline__ bool get_next_item(WorkItem& item) {
-        if constexpr (kGemmType == GemmType::Normal) {
-            if (split_pos < split_end) {
-                const uint32_t tile = split_pos / num_k_blocks;
-                item.kb_begin = split_pos - tile * num_k_blocks;
-                item.kb_end = min(num_k_blocks, item.kb_begin + (split_end - split_pos));
-                split_pos += item.kb_end - item.kb_begin;
-                swizzle(tile, num_m_blocks, item.m_block_idx, item.n_block_idx);
-                if (item.kb_begin > 0) {  // the tile began in the previous CTA's share
-                    item.seam = static_cast<int>(blockIdx.x) - 1;
-                    item.part = 1;
-                } else if (item.kb_end < num_k_blocks) {  // it ends in the next CTA's share
-                    item.seam = static_cast<int>(blockIdx.x);
-                    item.part = 0;
-                } else {
-                    item.seam = -1;
-                    item.part = 0;
-                }
-                return true;
-            }
-            const uint32_t next = split_tiles + static_cast<uint32_t>(++current_iter) * gridDim.x + blockIdx.x;
-            if (next >= num_blocks) return false;
-            swizzle(next, num_m_blocks, item.m_block_idx, item.n_block_idx);
-        } else {
-            if (!get_next_block(item.m_block_idx, item.n_block_idx)) return false;
-        }
-        item.kb_begin = 0;
-        item.kb_end = num_k_blocks;
-        item.seam = -1;
-        item.part = 0;
-        return true;
     }
 
     // Band-major order: tiles of 16 consecutive m-blocks sweep all n-blocks before the next band

@@ -61,7 +61,7 @@ def get_smem_size(block_n: int, num_stages: int) -> int:
     num_tmem_bufs = 2 if block_n > 128 else 4
     ring = num_stages * (128 * 128 + block_n * 128)
     store = 8 * 2048 if ring + 8 * 2048 + 2048 <= 232448 else 0
-    return ring + store + (2 * num_stages + 4 * num_tmem_bufs + 1) * 8 + 12 + 1024
+    return ring + store + (2 * num_stages + 4 * num_tmem_bufs) * 8 + 8 + 1024
 
 
 # time of one tile relative to a 256-wide one (measured; see choose_block_n in csrc/capi.cu)
@@ -142,41 +142,8 @@ def gemm_fp8_fp8_bf16_nt(lhs: Tuple[torch.Tensor, torch.Tensor], rhs: Tuple[torc
             raise _lib.YanB200Error('gemm_fp8_fp8_bf16_nt[jit]', rc, 'see ReturnCode in include/gemm/utils.cuh')
         _jit_runtimes_used[runtime.path] = runtime
         return
-    if block_n == 0 and m > 64 and split_k_enabled():
-        # the library may cut the tiles of a nearly empty last wave along K (scratch per device and stream)
-        ws = _split_workspace(out.device, num_sms)
-        _lib.call("yan_b200_gemm_fp8_fp8_bf16_nt_split", lhs_q.data_ptr(), lhs_scales.data_ptr(), rhs_q.data_ptr(),
-                  rhs_scales.data_ptr(), out.data_ptr(), m, n, k, out.stride(0), _stream_ptr(), num_sms, block_n,
-                  ws.data_ptr(), ws.numel())
-        return
     _lib.call("yan_b200_gemm_fp8_fp8_bf16_nt", lhs_q.data_ptr(), lhs_scales.data_ptr(), rhs_q.data_ptr(),
               rhs_scales.data_ptr(), out.data_ptr(), m, n, k, out.stride(0), _stream_ptr(), num_sms, block_n)
-
-
-_split_workspaces = {}
-_split_k = [True]
-
-
-def split_k_enabled() -> bool:
-    return _split_k[0]
-
-
-def set_split_k(enabled: bool) -> None:
-    """Lets gemm_fp8_fp8_bf16_nt(block_n=0) cut the tiles of a nearly empty last wave along K (default on).  Off, or
-    with an explicit block_n, every tile is computed whole by one CTA and the result does not depend on the grid."""
-    _split_k[0] = bool(enabled)
-
-
-def _split_workspace(device: torch.device, num_sms: int) -> torch.Tensor:
-    """Zeroed scratch for the split tiles, one per (device, stream, grid): launches on one stream are ordered, launches on
-    different streams must not share a workspace."""
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream, num_sms)
-    ws = _split_workspaces.get(key)
-    if ws is None:
-        need = int(_lib.lib().yan_b200_gemm_split_workspace_bytes(num_sms))
-        ws = torch.zeros(need, dtype=torch.uint8, device=device)
-        _split_workspaces[key] = ws
-    return ws
 
 
 def gemm_fp8_fp8_f32_nt(lhs, rhs, out: torch.Tensor, block_n: int = 0) -> None:
