@@ -61,6 +61,23 @@ void yan_b200_gemm_fp8_fp8_bf16_nt(const void* lhs, const void* lhs_scales, cons
                                    void* out, int m, int n, int k, int ldd, void* stream, int num_sms, int block_n,
                                    int* return_code);
 
+/*
+ * The same GEMM, allowed to cut the tiles of a nearly empty last wave along K.  896 tiles on 148 SMs run as 7 waves
+ * for 6.05 waves of work; with a workspace the launch becomes three: the whole-tile kernel over the full waves, a
+ * second instance of it in which every CTA computes one K-slice of one of the remaining tiles into an fp32 partial
+ * tile, and a small kernel that adds a tile's partials in slice order, rounds once and stores.  The result can differ
+ * from yan_b200_gemm_fp8_fp8_bf16_nt in the last bit of those tiles (a sum of partial sums instead of one running
+ * sum) and meets the same tolerance against the dequantize-and-matmul result; it does not depend on timing.
+ * workspace: device memory, 256-byte aligned, at least yan_b200_gemm_tail_workspace_bytes(num_sms) bytes, contents
+ * irrelevant; NULL = whole tiles only.  Two launches that may run at the same time need a workspace each.
+ * Extends the persistent scheduler the reference sketches (yan/include/gemm/scheduler.cuh:20,39-41), which only
+ * knows whole tiles.
+ */
+size_t yan_b200_gemm_tail_workspace_bytes(int num_sms);
+void yan_b200_gemm_fp8_fp8_bf16_nt_tail(const void* lhs, const void* lhs_scales, const void* rhs, const void* rhs_scales,
+                                        void* out, int m, int n, int k, int ldd, void* stream, int num_sms, int block_n,
+                                        void* workspace, size_t workspace_bytes, int* return_code);
+
 /* Same GEMM with the next layer's quantizer fused into the epilogue: out = e4m3 [M, ldd] (ldd % 16 == 0, 16-byte
  * aligned) and out_scales = fp32, k-block-major [N/128][out_scales_ld] (out_scales_ld >= m), i.e. exactly what
  * yan_b200_per_token_cast_to_fp8 would produce from the bf16 output of yan_b200_gemm_fp8_fp8_bf16_nt (the accumulator is

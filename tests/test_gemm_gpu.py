@@ -273,3 +273,38 @@ def test_host_front_end_pipelines_three_calls(cuda_lib):
     pipe.wait()
     for a, o in zip(ins, outs):
         _check(o, ref.ref_gemm(ref.per_token_cast_to_fp8(a), rhs), "host front end")
+
+
+@pytest.mark.parametrize("num_sms", [148, 100])
+def test_tail_cut_along_k_matches_oracle_and_whole_tile_kernel(cuda_lib, num_sms):
+    """160 tiles of 128 x 256 on 148 (or 100) CTAs: the last wave would be nearly empty, so the automatic policy computes
+    the full waves as whole tiles, cuts the remaining tiles along K across all CTAs (fp32 partial tiles in a workspace)
+    and sums the partials in slice order.  Checked against the CPU oracle, against the whole-tile kernel (last-bit
+    differences only), twice on the same workspace, and for run-to-run reproducibility."""
+    import yan_b200
+    from yan_b200.jit_kernels.utils import get_num_sms, set_num_sms
+    m, n, k = 2048, 2560, 12288  # 96 k-blocks: the policy only cuts when K is long
+    a, b = ref.make_inputs(m, n, k, seed=41)
+    lhs, rhs = ref.per_token_cast_to_fp8(a), ref.per_block_cast_to_fp8(b)
+    d_ref = ref.ref_gemm(lhs, rhs)
+    lhs_d = (lhs[0].cuda(), lhs[1].t().contiguous().cuda().t())
+    rhs_d = (rhs[0].cuda(), rhs[1].cuda())
+    whole = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    yan_b200.gemm_fp8_fp8_bf16_nt(lhs_d, rhs_d, whole, block_n=256)
+    sms_before = get_num_sms()
+    try:
+        set_num_sms(min(num_sms, sms_before))
+        results = []
+        for attempt in range(2):
+            out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+            yan_b200.gemm_fp8_fp8_bf16_nt(lhs_d, rhs_d, out)
+            torch.cuda.synchronize()
+            assert yan_b200.read_device_status() == 0
+            assert not torch.isnan(out.float()).any(), f"attempt {attempt}: a tile was never stored"
+            assert ref.rel_frobenius(out.cpu(), d_ref) <= 1e-3
+            assert ref.max_abs_err(out.cpu(), d_ref) <= ref.bf16_ulp_at(float(d_ref.float().abs().max()))
+            assert ref.rel_frobenius(out.cpu(), whole.cpu()) <= 1e-4
+            results.append(out)
+        assert torch.equal(results[0], results[1])
+    finally:
+        set_num_sms(sms_before)

@@ -12,7 +12,7 @@ from .jit_kernels import (ceil_div, fp8_linear, fp8_linear_workspace_bytes, gemm
                           get_col_major_tensor, get_m_alignment_for_contiguous_layout, get_num_sms,
                           m_grouped_gemm_fp8_fp8_bf16_nt_contiguous, m_grouped_gemm_fp8_fp8_bf16_nt_masked,
                           per_block_cast_to_fp8, per_token_cast_to_fp8, read_device_status, set_num_sms,
-                          set_programmatic_dependent_launch, set_clock_probe, effective_sm_clock_mhz)
+                          set_programmatic_dependent_launch, set_clock_probe, effective_sm_clock_mhz, set_tail_cut)
 from .jit_kernels import HostFp8Linear
 from .utils import bench_events, bench_kineto, calc_diff, count_bytes, perf_log
 

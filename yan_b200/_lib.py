@@ -25,6 +25,8 @@ SIGNATURES = {
     "yan_b200_abi_version": (_I, []),
     "yan_b200_return_code_string": (ctypes.c_char_p, [_I]),
     "yan_b200_gemm_fp8_fp8_bf16_nt": (None, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _RC]),
+    "yan_b200_gemm_tail_workspace_bytes": (ctypes.c_size_t, [_I]),
+    "yan_b200_gemm_fp8_fp8_bf16_nt_tail": (None, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _P, ctypes.c_size_t, _RC]),
     "yan_b200_gemm_fp8_fp8_f32_nt": (None, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _RC]),
     "yan_b200_gemm_fp8_fp8_e4m3_nt": (None, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _RC]),
     "yan_b200_m_grouped_gemm_fp8_fp8_bf16_nt_contiguous": (None, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _RC]),

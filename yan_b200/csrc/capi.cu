@@ -91,7 +91,7 @@ inline void set_rc(int* rc, int v) {
 // part, so a narrower tile is far from proportionally cheaper, and the widths whose half does not divide 128 pay for a
 // second B scale and a 16-column tail chunk.  Large problems therefore get 256; narrower tiles win when they fill the
 // machine better (few tiles, or a last wave of 256-wide tiles that is nearly empty).
-int choose_block_n(int m, int n, int num_sms) {
+int choose_block_n(int m, int n, int k, int num_sms, bool can_cut_tail) {
     static const struct { int bn; double tile_cost; } candidates[8] = {
         {256, 1.000}, {224, 1.02}, {192, 0.83}, {160, 0.79}, {128, 0.63}, {96, 0.62}, {64, 0.50}, {32, 0.47}};
     int best = 256;
@@ -99,8 +99,12 @@ int choose_block_n(int m, int n, int num_sms) {
     for (const auto& c : candidates) {
         if (c.bn > 32 && n < c.bn) continue;
         const long tiles = static_cast<long>((m + 127) / 128) * ((n + c.bn - 1) / c.bn);
-        const long waves = (tiles + num_sms - 1) / num_sms;
-        const double cost = static_cast<double>(waves) * c.tile_cost;
+        double waves = static_cast<double>((tiles + num_sms - 1) / num_sms);
+        // with scratch for partial tiles the rest of a nearly empty last wave is cut along K (about a third of a wave)
+        if (can_cut_tail && (c.bn == 256 || c.bn == 128 || c.bn == 64) &&
+            yan::choose_tail_slices(static_cast<uint32_t>(tiles), static_cast<uint32_t>(num_sms), static_cast<uint32_t>(k / 128)) != 0)
+            waves = static_cast<double>(tiles / num_sms) + 0.35;
+        const double cost = waves * c.tile_cost;
         if (best_cost < 0.0 || cost < best_cost * 0.98) {  // a narrower tile must win by 2 % to be taken
             best_cost = cost;
             best = c.bn;
@@ -116,7 +120,8 @@ int dispatch_gemm(yan::GemmType type, yan::OutKind out_kind, yan::GemmArgs& a, i
     const bool want_auto = (block_n == 0);
     if (block_n == 0) {
         const int rows = (type == yan::GemmType::GroupedMasked) ? static_cast<int>(a.m * a.num_groups) : static_cast<int>(a.m);
-        block_n = choose_block_n(rows, static_cast<int>(a.n), a.num_sms);
+        block_n = choose_block_n(rows, static_cast<int>(a.n), static_cast<int>(a.k), a.num_sms,
+                                 type == yan::GemmType::Normal && out_kind == yan::OutKind::BF16 && a.tail_workspace != nullptr);
     }
     a.status = status_word_of_current_device();
     a.timeout_ns = g_timeout_ns;
@@ -214,6 +219,32 @@ YAN_EXPORT void yan_b200_gemm_fp8_fp8_bf16_nt(const void* lhs, const void* lhs_s
     a.ldd = static_cast<uint32_t>(ldd);
     a.m = m, a.n = n, a.k = k;
     a.num_sms = num_sms;
+    set_rc(return_code, dispatch_gemm(yan::GemmType::Normal, yan::OutKind::BF16, a, block_n, stream));
+}
+
+YAN_EXPORT size_t yan_b200_gemm_tail_workspace_bytes(int num_sms) {
+    return num_sms > 0 ? yan::tail_workspace_bytes(static_cast<uint32_t>(num_sms), 256) : 0;
+}
+
+YAN_EXPORT void yan_b200_gemm_fp8_fp8_bf16_nt_tail(const void* lhs, const void* lhs_scales, const void* rhs,
+                                                   const void* rhs_scales, void* out, int m, int n, int k, int ldd,
+                                                   void* stream, int num_sms, int block_n, void* workspace,
+                                                   size_t workspace_bytes, int* return_code) {
+    if (!positive(m, n, k) || ldd <= 0) return set_rc(return_code, yan::kBadArgument);
+    if (workspace != nullptr && reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+        return set_rc(return_code, yan::kBadArgument);
+    yan::GemmArgs a;
+    a.lhs = lhs;
+    a.lhs_scales = static_cast<const float*>(lhs_scales);
+    a.lhs_scales_ld = static_cast<uint32_t>(m);
+    a.rhs = rhs;
+    a.rhs_scales = static_cast<const float*>(rhs_scales);
+    a.out = out;
+    a.ldd = static_cast<uint32_t>(ldd);
+    a.m = m, a.n = n, a.k = k;
+    a.num_sms = num_sms;
+    a.tail_workspace = workspace;
+    a.tail_workspace_bytes = workspace_bytes;
     set_rc(return_code, dispatch_gemm(yan::GemmType::Normal, yan::OutKind::BF16, a, block_n, stream));
 }
 

@@ -48,6 +48,11 @@ struct GemmParams {
     uint32_t shape_n;
     uint32_t shape_k;
     uint32_t num_groups;
+    // Whole-tile launch: only tiles [0, tile_limit) of the scheduler's order are computed (0 = all).
+    // Tail launch (kTail instance): CTA b computes k-blocks slice b % tail_slices of tile tail_first_tile + b / tail_slices
+    // and writes its fp32 partial tile to slot (b % tail_slices) * tail_tiles + b / tail_slices of `out`.
+    uint32_t tile_limit = 0;
+    uint32_t tail_first_tile = 0, tail_tiles = 0, tail_slices = 0;
     int* status;  // optional device word: 0 = fine, otherwise (kDeviceTimeout << 8) | site
     unsigned long long timeout_ns;
     // optional: CTA 0 writes {clock64, globaltimer} when it starts and when it ends (4 values), so that the host can
@@ -217,7 +222,14 @@ struct GemmSmemLayout {
 #define YAN_STAMP_ADD(acc, from, to)
 #endif
 
-template <uint32_t BLOCK_N, uint32_t kNumStages, GemmType kGemmType, typename out_t>
+// kTail: the instance that finishes a launch whose last wave would be nearly empty.  With T tiles on G CTAs and
+// r = T mod G small, the whole-tile instance computes the first T - r tiles (full waves) and this one computes the last
+// r: every tile is cut along K into floor(G / r) slices, one CTA per (tile, slice), each writing an fp32 partial tile;
+// reduce_tail_partials_kernel then adds a tile's partials in slice order, rounds once and stores.  It is a separate
+// instance (and the k-range, tile choice and output slot are compile-time branches) because the code of the hot loop
+// is sensitive to everything else the kernel holds: an earlier form that taught the one kernel to cut tiles lost a
+// fifth of the whole-tile schedule's speed.
+template <uint32_t BLOCK_N, uint32_t kNumStages, GemmType kGemmType, typename out_t, bool kTail = false>
 __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     fp8_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tensor_map_a,
                     const __grid_constant__ CUtensorMap tensor_map_b) {
@@ -270,6 +282,23 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     const uint32_t lane_idx = ptx::lane_id();
     const uint32_t num_k_blocks = p.shape_k / kBlockK;
     const uint32_t num_sb_rows = ceil_div(p.shape_n, 128u);
+    static_assert(!kTail || (kGemmType == GemmType::Normal && sizeof(out_t) == 4), "the tail instance writes fp32 partials");
+    // k-blocks [kb_begin, kb_begin + kb_count) of every tile this CTA computes: all of them, or the CTA's slice
+    const uint32_t tail_slice = kTail ? blockIdx.x % p.tail_slices : 0u, tail_tile = kTail ? blockIdx.x / p.tail_slices : 0u;
+    const uint32_t kb_begin = kTail ? (tail_slice * num_k_blocks) / p.tail_slices : 0u;
+    const uint32_t kb_count = kTail ? ((tail_slice + 1) * num_k_blocks) / p.tail_slices - kb_begin : num_k_blocks;
+    // next tile of this CTA: the persistent walk, or the tail instance's single tile
+    [[maybe_unused]] bool tail_taken = false;
+    auto next_tile = [&](Sched& sched, uint32_t& m_block_idx, uint32_t& n_block_idx) -> bool {
+        if constexpr (kTail) {
+            if (tail_taken || tail_tile >= p.tail_tiles) return false;
+            tail_taken = true;
+            sched.swizzle(p.tail_first_tile + tail_tile, sched.num_m_blocks, m_block_idx, n_block_idx);
+            return true;
+        } else {
+            return sched.get_next_block(m_block_idx, n_block_idx);
+        }
+    };
 
     if (warp_idx == 0 && lane_idx == 0) {
         ptx::tma_prefetch_desc(&tensor_map_a);
@@ -309,15 +338,16 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
         if (warp_idx == 0 && lane_idx == 0) {
             // ------------------------------ TMA producer ------------------------------
             Sched sched(p.shape_m, p.shape_n, p.grouped_layout, p.num_groups);
+            if (p.tile_limit != 0) sched.num_blocks = min(sched.num_blocks, p.tile_limit);
             uint32_t m_block_idx, n_block_idx, stage = 0, phase = 0;
             bool alive = true;
             [[maybe_unused]] long long waited_empty = 0;
-            while (alive && sched.get_next_block(m_block_idx, n_block_idx)) {
+            while (alive && next_tile(sched, m_block_idx, n_block_idx)) {
                 const int group = sched.get_group(m_block_idx);
                 if (group < 0) continue;
                 const int32_t a_row = static_cast<int32_t>(sched.get_row_base(m_block_idx));
                 const int32_t b_row = static_cast<int32_t>(group * p.shape_n + n_block_idx * BLOCK_N);
-                for (uint32_t kb = 0; kb < num_k_blocks; ++kb) {
+                for (uint32_t kb = kb_begin; kb < kb_begin + kb_count; ++kb) {
                     YAN_STAMP(w0);
                     if (!detail::bounded_wait(empty_barriers + stage, phase ^ 1, abort_flag, p, 1)) {
                         alive = false;
@@ -348,6 +378,7 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
         } else if (warp_idx == 1 && lane_idx == 0) {
             // ------------------------------ MMA issuer ------------------------------
             Sched sched(p.shape_m, p.shape_n, p.grouped_layout, p.num_groups);
+            if (p.tile_limit != 0) sched.num_blocks = min(sched.num_blocks, p.tile_limit);
             constexpr uint32_t kUmmaN = BLOCK_N / kNumHalves;
             constexpr uint32_t idesc = make_instr_desc_e4m3_f32(kBlockM, kUmmaN);
             // rows [kUmmaN, BLOCK_N) of the B tile start kUmmaN 128-byte rows further on (whole 8-row swizzle atoms)
@@ -357,9 +388,9 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
             bool alive = true;
             [[maybe_unused]] long long waited_full = 0, waited_tmem = 0;
             YAN_STAMP(mma_begin);
-            while (alive && sched.get_next_block(m_block_idx, n_block_idx)) {
+            while (alive && next_tile(sched, m_block_idx, n_block_idx)) {
                 if (sched.get_group(m_block_idx) < 0) continue;
-                for (uint32_t kb = 0; kb < num_k_blocks && alive; ++kb) {
+                for (uint32_t kb = 0; kb < kb_count && alive; ++kb) {
                     YAN_STAMP(w0);
                     if (!detail::bounded_wait(full_barriers + stage, phase, abort_flag, p, 2)) {
                         alive = false;
@@ -421,47 +452,50 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
         const uint32_t half = kSplitHalves ? wg : 0;
 
         Sched sched(p.shape_m, p.shape_n, p.grouped_layout, p.num_groups);
+        if (p.tile_limit != 0) sched.num_blocks = min(sched.num_blocks, p.tile_limit);
         uint32_t m_block_idx, n_block_idx, buf = 0, buf_phase = 0;
         bool alive = true, next_ready = false;
         float acc[kColsPerWG];
         [[maybe_unused]] long long waited_tmem_full = 0, in_loads = 0, in_fmas = 0, in_stores = 0, promoted = 0;
         YAN_STAMP(promo_begin);
 
-        while (alive && sched.get_next_block(m_block_idx, n_block_idx)) {
+        while (alive && next_tile(sched, m_block_idx, n_block_idx)) {
             const int group = sched.get_group(m_block_idx);
             if (group < 0) continue;
             const uint32_t row = sched.get_row_base(m_block_idx) + row_in_tile;
             const bool row_ok = row < sched.get_row_limit();
             const uint32_t n_first = n_block_idx * BLOCK_N + col0;
             const uint32_t sb_row = min(n_first / 128u, num_sb_rows - 1);
-            const float* sa_ptr = p.scales_a + row;
-            const float* sb_ptr = p.scales_b + (static_cast<size_t>(group) * num_sb_rows + sb_row) * num_k_blocks;
+            const float* sa_ptr = p.scales_a + (kTail ? static_cast<size_t>(kb_begin) * p.sa_ld : 0) + row;
+            const float* sb_ptr =
+                p.scales_b + (static_cast<size_t>(group) * num_sb_rows + sb_row) * num_k_blocks + (kTail ? kb_begin : 0u);
             const float* sa_next = sa_ptr + static_cast<size_t>(kScaleDepth) * p.sa_ld;  // row's scale kScaleDepth k-blocks ahead
             // two-scale case: groups of 16 columns from `hi_from` on belong to the next 128-column block
             const uint32_t hi_from = kTwoScales ? (128u - n_first % 128u) / 16u : 0xFFFFu;
-            const float* sb_hi_ptr =
-                p.scales_b + (static_cast<size_t>(group) * num_sb_rows + min(sb_row + 1, num_sb_rows - 1)) * num_k_blocks;
+            const float* sb_hi_ptr = p.scales_b +
+                                     (static_cast<size_t>(group) * num_sb_rows + min(sb_row + 1, num_sb_rows - 1)) * num_k_blocks +
+                                     (kTail ? kb_begin : 0u);
 
             // Scales are prefetched kScaleDepth k-blocks ahead: one L2 round trip is longer than one k-block.
             float sa_ring[kScaleDepth], sb_ring[kScaleDepth], sb_hi_ring[kTwoScales ? kScaleDepth : 1];
 #pragma unroll
             for (uint32_t i = 0; i < kScaleDepth; ++i) {
-                sa_ring[i] = (row_ok && i < num_k_blocks) ? __ldg(sa_ptr + static_cast<size_t>(i) * p.sa_ld) : 0.0f;
-                sb_ring[i] = (i < num_k_blocks) ? __ldg(sb_ptr + i) : 0.0f;
-                if constexpr (kTwoScales) sb_hi_ring[i] = (i < num_k_blocks) ? __ldg(sb_hi_ptr + i) : 0.0f;
+                sa_ring[i] = (row_ok && i < kb_count) ? __ldg(sa_ptr + static_cast<size_t>(i) * p.sa_ld) : 0.0f;
+                sb_ring[i] = (i < kb_count) ? __ldg(sb_ptr + i) : 0.0f;
+                if constexpr (kTwoScales) sb_hi_ring[i] = (i < kb_count) ? __ldg(sb_hi_ptr + i) : 0.0f;
             }
 #pragma unroll
             for (uint32_t j = 0; j < kColsPerWG; ++j) acc[j] = 0.0f;
 
-            for (uint32_t kb0 = 0; kb0 < num_k_blocks && alive; kb0 += kScaleDepth) {
+            for (uint32_t kb0 = 0; kb0 < kb_count && alive; kb0 += kScaleDepth) {
 #pragma unroll
                 for (uint32_t i = 0; i < kScaleDepth; ++i) {
                     const uint32_t kb = kb0 + i;
-                    if (!alive || kb >= num_k_blocks) continue;
+                    if (!alive || kb >= kb_count) continue;
                     const float scale = sa_ring[i] * sb_ring[i];
                     float scale_hi = scale;
                     if constexpr (kTwoScales) scale_hi = sa_ring[i] * sb_hi_ring[i];
-                    if (kb + kScaleDepth < num_k_blocks) {
+                    if (kb + kScaleDepth < kb_count) {
                         sa_ring[i] = row_ok ? __ldg(sa_next) : 0.0f;
                         sa_next += p.sa_ld;
                         sb_ring[i] = __ldg(sb_ptr + kb + kScaleDepth);
@@ -552,8 +586,12 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
                     const uint32_t box = ptx::smem_u32(smem + L::kOffStore + (warp_idx - 4) * L::kStoreBoxBytes);
                     const uint32_t row_addr = box + lane_idx * 64u;
                     constexpr uint32_t kElemsPerChunk = 16 / sizeof(out_t);
-                    const uint32_t tile_row0 = sched.get_row_base(m_block_idx) + quarter * 32u;
-                    const uint32_t row_limit = sched.get_row_limit();
+                    // the tail instance writes whole partial tiles into its slot of the scratch: [slot][128][BLOCK_N]
+                    const uint32_t tile_row0 =
+                        (kTail ? (tail_slice * p.tail_tiles + tail_tile) * kBlockM : sched.get_row_base(m_block_idx)) + quarter * 32u;
+                    const uint32_t row_limit = kTail ? 0xFFFFFFFFu : sched.get_row_limit();
+                    const uint32_t out_ld = kTail ? BLOCK_N : p.ldd, out_cols = kTail ? BLOCK_N : p.shape_n;
+                    const uint32_t n_store = kTail ? col0 : n_first;
                     out_t* out_base = reinterpret_cast<out_t*>(p.out);
 #pragma unroll
                     for (uint32_t pass = 0; pass < kColsPerWG / kStoreCols; ++pass) {
@@ -577,14 +615,14 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
                         }
                         __syncwarp();
                         // read back: instruction i covers box rows 8i .. 8i+7, lane l -> row 8i + l/4, chunk l%4
-                        const uint32_t n_chunk = n_first + pass * kStoreCols + (lane_idx & 3u) * kElemsPerChunk;
+                        const uint32_t n_chunk = n_store + pass * kStoreCols + (lane_idx & 3u) * kElemsPerChunk;
 #pragma unroll
                         for (uint32_t i = 0; i < 4; ++i) {
                             const uint32_t r = i * 8u + (lane_idx >> 2);
                             const uint4 v = ptx::ld_shared_v4(box + r * 64u + (((lane_idx & 3u) ^ ((r >> 1) & 3u)) << 4));
                             const uint32_t out_row = tile_row0 + r;
-                            if (out_row < row_limit && n_chunk < p.shape_n)
-                                *reinterpret_cast<uint4*>(out_base + static_cast<size_t>(out_row) * p.ldd + n_chunk) = v;
+                            if (out_row < row_limit && n_chunk < out_cols)
+                                *reinterpret_cast<uint4*>(out_base + static_cast<size_t>(out_row) * out_ld + n_chunk) = v;
                         }
                     }
                 }
@@ -638,7 +676,65 @@ struct GemmArgs {
     int* status = nullptr;
     unsigned long long timeout_ns = 2000000000ull;
     long long* clock_probe = nullptr;  // optional: 4 values written by CTA 0 (see GemmParams)
+    // optional scratch (tail_workspace_bytes) that lets a Normal bf16 launch cut the tiles of a nearly empty last wave
+    // along K; its contents are rewritten by every launch that uses it, nothing needs to be cleared
+    void* tail_workspace = nullptr;
+    size_t tail_workspace_bytes = 0;
 };
+
+// Bytes of scratch a grid of `num_sms` CTAs can use for the tail of a launch of BLOCK_N-wide tiles.
+constexpr size_t tail_workspace_bytes(uint32_t num_sms, uint32_t block_n) {
+    return static_cast<size_t>(num_sms) * kBlockM * block_n * sizeof(float);
+}
+
+// How to finish `tiles` tiles on `grid` CTAs: slices per tile of the last `tiles % grid` tiles, or 0 to run them as one
+// more wave of whole tiles.  Cutting pays when that wave would be less than half full, costs at least 5 % of the launch,
+// and K is long: the two extra launches and the tail CTAs' prologue and epilogue cost about 25 us, which a wave of
+// 64 k-blocks (K = 8192, ~30 us) does not repay and a wave of 144 (K = 18432, ~70 us) does
+// (measured on B200: M=4096 N=7168 K=18432 533 -> 505 us; M=8192 N=3584 K=8192 230 -> 232 us).
+inline uint32_t choose_tail_slices(uint32_t tiles, uint32_t grid, uint32_t num_k_blocks) {
+    const uint32_t rest = tiles % grid;
+    if (grid < 2 || tiles < grid || rest == 0 || 2 * rest > grid || num_k_blocks < 96) return 0;
+    const uint32_t waves = tiles / grid + 1;
+    if (static_cast<double>(grid - rest) / (static_cast<double>(waves) * grid) < 0.05) return 0;
+    uint32_t slices = grid / rest;
+    if (slices > num_k_blocks / 3) slices = num_k_blocks / 3;
+    return slices >= 2 ? slices : 0;
+}
+
+// Adds the fp32 partial tiles of a tail launch in slice order, rounds once and stores bf16.  One thread per 8 columns.
+template <uint32_t BLOCK_N>
+__global__ void __launch_bounds__(256) reduce_tail_partials_kernel(const float* __restrict__ partials,
+                                                                    __nv_bfloat16* __restrict__ out, uint32_t ldd,
+                                                                    uint32_t shape_m, uint32_t shape_n, uint32_t first_tile,
+                                                                    uint32_t tail_tiles, uint32_t slices) {
+    constexpr uint32_t kChunksPerRow = BLOCK_N / 8;
+    const uint32_t t = blockIdx.x;
+    const uint32_t idx = blockIdx.y * 256 + threadIdx.x;
+    const uint32_t row = idx / kChunksPerRow, chunk = idx % kChunksPerRow;
+    if (row >= kBlockM) return;
+    Scheduler<GemmType::Normal, kBlockM, BLOCK_N> sched(shape_m, shape_n);
+    uint32_t m_block_idx, n_block_idx;
+    sched.swizzle(first_tile + t, sched.num_m_blocks, m_block_idx, n_block_idx);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (uint32_t sl = 0; sl < slices; ++sl) {
+        const float4* src = reinterpret_cast<const float4*>(
+            partials + (static_cast<size_t>(sl * tail_tiles + t) * kBlockM + row) * BLOCK_N + chunk * 8);
+        const float4 lo = __ldcg(src), hi = __ldcg(src + 1);
+        acc[0] += lo.x, acc[1] += lo.y, acc[2] += lo.z, acc[3] += lo.w;
+        acc[4] += hi.x, acc[5] += hi.y, acc[6] += hi.z, acc[7] += hi.w;
+    }
+    const uint32_t out_row = m_block_idx * kBlockM + row, out_col = n_block_idx * BLOCK_N + chunk * 8;
+    if (out_row >= shape_m || out_col >= shape_n) return;
+    uint4 v;
+    __nv_bfloat162 t0 = __floats2bfloat162_rn(acc[0], acc[1]), t1 = __floats2bfloat162_rn(acc[2], acc[3]);
+    __nv_bfloat162 t2 = __floats2bfloat162_rn(acc[4], acc[5]), t3 = __floats2bfloat162_rn(acc[6], acc[7]);
+    v.x = *reinterpret_cast<uint32_t*>(&t0);
+    v.y = *reinterpret_cast<uint32_t*>(&t1);
+    v.z = *reinterpret_cast<uint32_t*>(&t2);
+    v.w = *reinterpret_cast<uint32_t*>(&t3);
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(out_row) * ldd + out_col) = v;
+}
 
 inline bool is_aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
@@ -710,6 +806,35 @@ struct GemmLauncher {
         if (kGemmType != GemmType::GroupedMasked) {
             const uint32_t tiles = ceil_div(a.m, kBlockM) * ceil_div(a.n, BLOCK_N);
             grid = tiles < grid ? tiles : grid;
+        }
+        // A nearly empty last wave: whole tiles for the full waves, then the rest cut along K, then the sum of the cuts.
+        if constexpr (kGemmType == GemmType::Normal && sizeof(out_t) == 2 && L::kStoreBytes != 0) {
+            const uint32_t tiles = ceil_div(a.m, kBlockM) * ceil_div(a.n, BLOCK_N);
+            const uint32_t slices = (a.tail_workspace != nullptr && is_aligned(a.tail_workspace, 16))
+                                        ? choose_tail_slices(tiles, grid, a.k / kBlockK) : 0;
+            const uint32_t rest = tiles % grid;
+            if (slices != 0 && a.tail_workspace_bytes >= static_cast<size_t>(rest) * slices * kBlockM * BLOCK_N * sizeof(float)) {
+                auto tail_kernel = fp8_gemm_kernel<BLOCK_N, kNumStages, GemmType::Normal, float, true>;
+                if (cudaFuncSetAttribute(tail_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemSize) != cudaSuccess) {
+                    cudaGetLastError();
+                    return kSmemTooLarge;
+                }
+                p.tile_limit = tiles - rest;
+                kernel<<<grid, get_num_threads_per_sm<>(BLOCK_N), kSmemSize, stream>>>(p, map_a, map_b);
+                GemmParams tail = p;
+                tail.tile_limit = 0;
+                tail.out = a.tail_workspace;
+                tail.tail_first_tile = tiles - rest;
+                tail.tail_tiles = rest;
+                tail.tail_slices = slices;
+                tail.clock_probe = nullptr;
+                tail_kernel<<<rest * slices, get_num_threads_per_sm<>(BLOCK_N), kSmemSize, stream>>>(tail, map_a, map_b);
+                const dim3 reduce_grid(rest, kBlockM * (BLOCK_N / 8) / 256);
+                reduce_tail_partials_kernel<BLOCK_N><<<reduce_grid, 256, 0, stream>>>(
+                    static_cast<const float*>(a.tail_workspace), static_cast<__nv_bfloat16*>(a.out), a.ldd, a.m, a.n,
+                    tiles - rest, rest, slices);
+                return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+            }
         }
         kernel<<<grid, get_num_threads_per_sm<>(BLOCK_N), kSmemSize, stream>>>(p, map_a, map_b);
         return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;

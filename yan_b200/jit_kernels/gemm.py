@@ -142,8 +142,41 @@ def gemm_fp8_fp8_bf16_nt(lhs: Tuple[torch.Tensor, torch.Tensor], rhs: Tuple[torc
             raise _lib.YanB200Error('gemm_fp8_fp8_bf16_nt[jit]', rc, 'see ReturnCode in include/gemm/utils.cuh')
         _jit_runtimes_used[runtime.path] = runtime
         return
+    if block_n == 0 and m > 64 and tail_cut_enabled():
+        # the library may cut the tiles of a nearly empty last wave along K (scratch per device and stream)
+        ws = _tail_workspace(out.device, num_sms)
+        _lib.call("yan_b200_gemm_fp8_fp8_bf16_nt_tail", lhs_q.data_ptr(), lhs_scales.data_ptr(), rhs_q.data_ptr(),
+                  rhs_scales.data_ptr(), out.data_ptr(), m, n, k, out.stride(0), _stream_ptr(), num_sms, block_n,
+                  ws.data_ptr(), ws.numel())
+        return
     _lib.call("yan_b200_gemm_fp8_fp8_bf16_nt", lhs_q.data_ptr(), lhs_scales.data_ptr(), rhs_q.data_ptr(),
               rhs_scales.data_ptr(), out.data_ptr(), m, n, k, out.stride(0), _stream_ptr(), num_sms, block_n)
+
+
+_tail_workspaces = {}
+_tail_cut = [True]
+
+
+def tail_cut_enabled() -> bool:
+    return _tail_cut[0]
+
+
+def set_tail_cut(enabled: bool) -> None:
+    """Lets gemm_fp8_fp8_bf16_nt(block_n=0) cut the tiles of a nearly empty last wave along K (default on).  Off, or
+    with an explicit block_n, every tile is computed whole by one CTA and the result does not depend on the grid."""
+    _tail_cut[0] = bool(enabled)
+
+
+def _tail_workspace(device: torch.device, num_sms: int) -> torch.Tensor:
+    """Scratch for the partial tiles, one per (device, stream, grid): launches on one stream are ordered, launches on
+    different streams must not share a workspace."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream, num_sms)
+    ws = _tail_workspaces.get(key)
+    if ws is None:
+        need = int(_lib.lib().yan_b200_gemm_tail_workspace_bytes(num_sms))
+        ws = torch.empty(need, dtype=torch.uint8, device=device)
+        _tail_workspaces[key] = ws
+    return ws
 
 
 def gemm_fp8_fp8_f32_nt(lhs, rhs, out: torch.Tensor, block_n: int = 0) -> None:
