@@ -447,6 +447,17 @@ def bench_k_split(rank: int, world: int, dist, steps: int = 10) -> dict:
             comm_sw.close()
         except Exception as e:
             results["in-switch peer allreduce"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+        try:
+            from yan_b200.comm import TileFusedAllreduce
+            fused = TileFusedAllreduce(m, n)
+
+            def step():
+                yan_b200.per_token_cast_to_fp8(a, out=lhs)
+                fused.gemm_and_reduce(lhs, rhs)
+            results["tile-fused: reduce-scatter in the GEMM epilogue + all-gather kernel"] = _time_k_split(step, dist, steps, m, n, k)
+            fused.close()
+        except Exception as e:
+            results["tile-fused"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
         results["allreduce alone, NCCL"] = _time_k_split(lambda: dist.all_reduce(out), dist, steps, m, n, k, flops=False)
         results["allreduce alone, two-shot"] = _time_k_split(lambda: comm.reduce_rows(), dist, steps, m, n, k, flops=False)
         results["device_status"] = yan_b200.read_device_status()
@@ -543,6 +554,18 @@ def multi_gpu_parity(rank: int, world: int, dist) -> dict:
             comm.close()
     except Exception as e:
         out["peer_memory"] = {"unavailable": f"{type(e).__name__}: {e}"[:160]}
+    # the tile-fused form: reduce-scatter inside the GEMM epilogue, all-gather kernel behind it; same arithmetic as two-shot
+    try:
+        from yan_b200.comm import TileFusedAllreduce
+        fused = TileFusedAllreduce(m, n)
+        for attempt in range(2):  # twice: the staging arrays and epochs are reused
+            got = fused.gemm_and_reduce(lhs_k, rhs_k)
+            torch.cuda.synchronize()
+            record(f"k_split_tile_fused_call_{attempt + 1}", got, d_split, 2e-3,
+                   {"bit_exact_vs_fp32_rank_order_sum": bool(torch.equal(got, rank_order_sum))})
+        fused.close()
+    except Exception as e:
+        out["k_split_tile_fused"] = {"unavailable": f"{type(e).__name__}: {e}"[:160]}
     # the host front end with sharded input: the gathered operand must equal the quantizer's output on all of A
     pipe = yan_b200.HostFp8Linear(rhs_n, m, depth=1, shard_input=True)
     a_pinned = a.contiguous().pin_memory()

@@ -226,6 +226,25 @@ void yan_b200_allreduce_bf16_in_switch(void* multicast, void* const* signals, in
                                        int* return_code);
 
 /*
+ * Row-parallel (K-split) GEMM fused with its allreduce, tile by tile: what comm/gemm_allreduce.cu:339-410 does with
+ * NVSHMEM tile collectives, on plain peer-mapped memory.
+ *   _scatter: the GEMM of one rank's K shard; its epilogue stores every finished bf16 tile of m-block mb into the staging
+ *             array of the rank that owns it, rank mb % world, at [rank][row][col] (stage[r]: rank r's
+ *             [world][M][ldd] bf16 array as mapped into this process, 16-byte aligned) -- the reduce-scatter half of the
+ *             allreduce, overlapped with the MMAs of the following tiles.  block_n 0, 128 or 256.
+ *   _gather_staged: every rank sums, for the m-blocks it owns, the `world` staged copies (fp32 in rank order, one
+ *             rounding: the two-shot kernel's arithmetic, bit for bit) and stores the rows to all ranks' outputs
+ *             (data[r]: rank r's [rows][ld] bf16 buffer).  signals / epoch / counter_target as for the two-shot kernel
+ *             (epoch > 0: the entry barrier is what tells a rank that every peer's tiles have landed).
+ */
+void yan_b200_gemm_fp8_fp8_bf16_nt_scatter(const void* lhs, const void* lhs_scales, const void* rhs, const void* rhs_scales,
+                                           void* const* stage, int world, int rank, int m, int n, int k, int ldd,
+                                           void* stream, int num_sms, int block_n, int* return_code);
+void yan_b200_allreduce_bf16_gather_staged(const void* stage, void* const* data, void* const* signals, int world, int rank,
+                                           int rows, int ld, unsigned int epoch, unsigned int counter_target,
+                                           int num_ctas, void* stream, int* return_code);
+
+/*
  * Programmatic dependent launch for the weight-streaming (M <= 64) kernel.  When enabled, that kernel is
  * launched with cudaLaunchAttributeProgrammaticStreamSerialization: its weight loads (rhs) may start while the
  * previous kernel of the stream is still running; activations, scales of the activations and the output are

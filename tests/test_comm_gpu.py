@@ -139,6 +139,23 @@ def _two_shot_worker(rank, world, port, results):
                     checks[f"{tag}: K-split {chunks} chunk(s) vs NCCL"] = bool(torch.equal(out, nccl))
             checks[f"{tag}: status"] = yan_b200.read_device_status() == 0
             comm.close()
+        # the tile-fused form (reduce-scatter in the GEMM epilogue, all-gather kernel): same sum as the two-shot kernel
+        from yan_b200.comm import TileFusedAllreduce
+        partial = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+        yan_b200.gemm_fp8_fp8_bf16_nt(lhs_local, rhs_k, partial, block_n=256)
+        gathered = [torch.empty_like(partial) for _ in range(world)]
+        dist.all_gather(gathered, partial)
+        acc = torch.zeros(m, n, dtype=torch.float32, device="cuda")
+        for g in gathered:
+            acc += g.float()
+        fused = TileFusedAllreduce(m, n)
+        for call in range(3):
+            got = fused.gemm_and_reduce(lhs_local, rhs_k)
+            torch.cuda.synchronize()
+            checks[f"tile-fused call {call}: equals the fp32 rank-order sum"] = bool(torch.equal(got, acc.to(torch.bfloat16)))
+            checks[f"tile-fused call {call}: vs oracle"] = ref.rel_frobenius(got.cpu(), d_split) <= 2e-3
+        checks["tile-fused: status"] = yan_b200.read_device_status() == 0
+        fused.close()
         results[rank] = {name: bool(v) for name, v in checks.items()}
     finally:
         dist.destroy_process_group()

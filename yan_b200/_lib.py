@@ -41,6 +41,10 @@ SIGNATURES = {
                                                 _I, _P, _RC]),
     "yan_b200_allreduce_bf16_in_switch": (None, [_P, ctypes.POINTER(ctypes.c_void_p), _I, _I, ctypes.c_ulonglong,
                                                  ctypes.c_ulonglong, ctypes.c_uint, ctypes.c_uint, _I, _I, _P, _RC]),
+    "yan_b200_gemm_fp8_fp8_bf16_nt_scatter": (None, [_P, _P, _P, _P, ctypes.POINTER(ctypes.c_void_p), _I, _I, _I, _I, _I, _I, _P,
+                                                     _I, _I, _RC]),
+    "yan_b200_allreduce_bf16_gather_staged": (None, [_P, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p), _I, _I,
+                                                     _I, _I, ctypes.c_uint, ctypes.c_uint, _I, _P, _RC]),
     "yan_b200_fp8_linear_workspace_bytes": (ctypes.c_size_t, [_I, _I]),
     "yan_b200_fp8_linear_bf16": (None, [_P, _P, _P, _P, _P, ctypes.c_size_t, _I, _I, _I, _I, _P, _I, _I, _RC]),
     "yan_b200_fp8_linear_bf16_static": (None, [_P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _RC]),

@@ -219,3 +219,67 @@ class TwoShotAllreduce:
 
     def close(self) -> None:
         self._arena.close()
+
+
+class TileFusedAllreduce:
+    """The K-split GEMM fused with its allreduce, tile by tile (the shape of the reference's epilogue,
+    comm/gemm_allreduce.cu:339-410, without NVSHMEM).
+
+    `gemm_and_reduce(lhs_shard, rhs_shard)` runs this rank's K shard of the GEMM; the epilogue stores every finished bf16
+    tile into the staging array of the rank that owns its m-block (`stage`, [world, M, N], peer-mapped) while the MMAs of
+    the next tiles run -- the reduce-scatter half of the allreduce costs no time of its own.  A second kernel then sums,
+    on every rank, the `world` staged copies of the rows it owns (fp32 in rank order, one rounding: bit-identical to
+    TwoShotAllreduce) and stores them into all ranks' `buffer` -- the all-gather half.  Every rank makes the same calls in
+    the same order."""
+
+    def __init__(self, m: int, n: int, group: Optional[dist.ProcessGroup] = None, num_ctas: Optional[int] = None):
+        assert n % 8 == 0 and m % 128 == 0
+        self.group = group
+        self.m, self.n = m, n
+        world = dist.get_world_size(group)
+        assert 2 <= world <= 8
+        tensor_bytes = m * n * 2
+        stage_offset = -(-(tensor_bytes + SIGNAL_BYTES) // 256) * 256
+        self._arena = PeerSharedTensor((stage_offset + world * tensor_bytes,), torch.uint8, group)
+        self.rank, self.world = self._arena.rank, self._arena.world
+        self.buffer = self._arena.local[:tensor_bytes].view(torch.bfloat16).view(m, n)
+        self.stage = self._arena.local[stage_offset:].view(torch.bfloat16).view(world, m, n)
+        self._data = self._arena.ptr_array()
+        self._signals = (ctypes.c_void_p * self.world)(*[p + tensor_bytes for p in self._arena.ptrs])
+        self._stage = (ctypes.c_void_p * self.world)(*[p + stage_offset for p in self._arena.ptrs])
+        sms = torch.cuda.get_device_properties(self.buffer.device).multi_processor_count
+        self.num_ctas = num_ctas or sms
+        self._clock = CollectiveClock()
+
+    def gemm_and_reduce(self, lhs_shard, rhs_shard, block_n: int = 0) -> torch.Tensor:
+        from ..jit_kernels.utils import get_col_major_tensor, get_num_sms
+        lhs_q, lhs_scales = lhs_shard
+        rhs_q, rhs_scales = rhs_shard
+        m, k = lhs_q.shape
+        assert (m, rhs_q.shape[0]) == (self.m, self.n) and rhs_q.shape[1] == k and k % 128 == 0
+        assert lhs_q.dtype == torch.float8_e4m3fn and rhs_q.dtype == torch.float8_e4m3fn
+        assert lhs_q.is_contiguous() and rhs_q.is_contiguous() and rhs_scales.is_contiguous()
+        lhs_scales = get_col_major_tensor(lhs_scales)
+        if lhs_scales.stride(1) != m:
+            lhs_scales = lhs_scales.t().contiguous().t()
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        _lib.call("yan_b200_gemm_fp8_fp8_bf16_nt_scatter", lhs_q.data_ptr(), lhs_scales.data_ptr(), rhs_q.data_ptr(),
+                  rhs_scales.data_ptr(), self._stage, self.world, self.rank, m, self.n, k, self.n, stream, get_num_sms(),
+                  block_n)
+        epoch, counter_target = self._clock.next_launch(self.num_ctas)
+        _lib.call("yan_b200_allreduce_bf16_gather_staged", ctypes.c_void_p(self.stage.data_ptr()), self._data, self._signals,
+                  self.world, self.rank, self.m, self.n, epoch, counter_target, self.num_ctas, stream)
+        return self.buffer
+
+    def reset(self) -> None:
+        """Collective; after a reported wait expiry: zero the signal blocks and restart the epochs."""
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        tensor_bytes = self.m * self.n * 2
+        self._arena.local[tensor_bytes:tensor_bytes + SIGNAL_BYTES].zero_()
+        self._clock.reset()
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+
+    def close(self) -> None:
+        self._arena.close()

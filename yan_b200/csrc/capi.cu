@@ -511,6 +511,54 @@ YAN_EXPORT void yan_b200_allreduce_bf16_in_switch(void* multicast, void* const* 
     set_rc(return_code, yan::launch_two_shot_allreduce_bf16(a, static_cast<cudaStream_t>(stream)));
 }
 
+YAN_EXPORT void yan_b200_gemm_fp8_fp8_bf16_nt_scatter(const void* lhs, const void* lhs_scales, const void* rhs,
+                                                      const void* rhs_scales, void* const* stage, int world, int rank,
+                                                      int m, int n, int k, int ldd, void* stream, int num_sms, int block_n,
+                                                      int* return_code) {
+    if (!positive(m, n, k) || ldd <= 0 || stage == nullptr || world < 2 || world > yan::kMaxPeers || rank < 0 || rank >= world)
+        return set_rc(return_code, yan::kBadArgument);
+    if (block_n != 0 && block_n != 256 && block_n != 128) return set_rc(return_code, yan::kBadArgument);
+    yan::GemmArgs a;
+    a.lhs = lhs;
+    a.lhs_scales = static_cast<const float*>(lhs_scales);
+    a.lhs_scales_ld = static_cast<uint32_t>(m);
+    a.rhs = rhs;
+    a.rhs_scales = static_cast<const float*>(rhs_scales);
+    a.out = stage[rank];  // every tile goes to a staging array; `out` only has to be a valid pointer
+    a.ldd = static_cast<uint32_t>(ldd);
+    a.m = m, a.n = n, a.k = k;
+    a.num_sms = num_sms;
+    for (int r = 0; r < world; ++r) a.scatter_base[r] = stage[r];
+    a.scatter_world = static_cast<uint32_t>(world);
+    a.scatter_rank = static_cast<uint32_t>(rank);
+    // the staged epilogue exists for the 256- and 128-wide tiles; the general width choice may pick others
+    set_rc(return_code, dispatch_gemm(yan::GemmType::Normal, yan::OutKind::BF16, a, block_n == 0 ? 256 : block_n, stream));
+}
+
+YAN_EXPORT void yan_b200_allreduce_bf16_gather_staged(const void* stage, void* const* data, void* const* signals,
+                                                      int world, int rank, int rows, int ld, unsigned int epoch,
+                                                      unsigned int counter_target, int num_ctas, void* stream,
+                                                      int* return_code) {
+    if (stage == nullptr || data == nullptr || signals == nullptr || world < 2 || world > yan::kMaxPeers || rows <= 0 || ld <= 0)
+        return set_rc(return_code, yan::kBadArgument);
+    yan::AllreduceArgs a;
+    for (int r = 0; r < world; ++r) {
+        a.data.p[r] = data[r];
+        a.signals.p[r] = signals[r];
+    }
+    a.world = world;
+    a.rank = rank;
+    a.epoch = epoch;
+    a.counter_target = counter_target;
+    a.num_ctas = num_ctas;
+    a.status = status_word_of_current_device();
+    a.timeout_ns = g_collective_timeout_ns;
+    a.stage = stage;
+    a.rows = static_cast<uint32_t>(rows);
+    a.ld = static_cast<uint32_t>(ld);
+    set_rc(return_code, yan::launch_gather_staged_allreduce_bf16(a, static_cast<cudaStream_t>(stream)));
+}
+
 YAN_EXPORT void yan_b200_set_programmatic_dependent_launch(int enabled) { g_programmatic_launch = enabled; }
 
 YAN_EXPORT void yan_b200_set_clock_probe(void* device_buffer) { g_clock_probe = static_cast<long long*>(device_buffer); }

@@ -216,7 +216,12 @@ __global__ void __launch_bounds__(kThreads)
     const size_t per_rank = (vec_count + W - 1) / W;
     const size_t first = vec_begin + static_cast<size_t>(rank) * per_rank;
     const size_t last = (first + per_rank < vec_begin + vec_count) ? first + per_rank : vec_begin + vec_count;
-    constexpr int kUnroll = 4;
+    // vectors in flight per thread: the switch answers a reducing load after a round trip through every peer's memory,
+    // so the kernel is bound by how many of them are outstanding, not by link bandwidth
+#ifndef YAN_IN_SWITCH_UNROLL
+#define YAN_IN_SWITCH_UNROLL 8
+#endif
+    constexpr int kUnroll = YAN_IN_SWITCH_UNROLL;
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
     for (size_t i0 = first + static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < last;
          i0 += stride * kUnroll) {
@@ -243,6 +248,73 @@ __global__ void __launch_bounds__(kThreads)
     if (epoch != 0) leave_collective<W>(signals, my_signals, rank, epoch, counter_target, status, timeout_ns);
 }
 
+// Second half of the allreduce whose first half ran inside the GEMM epilogue (fp8_gemm_kernel's scatter instance): the
+// tiles of m-block mb were stored by every rank into the staging array of rank mb % W, at [source rank][row][col].
+// This kernel sums, for the rows this rank owns, the W staged copies (local loads only; fp32 in rank order, one
+// rounding -- the arithmetic of the two-shot kernel, bit for bit) and stores the result to the same rows of all W
+// output buffers.  Per GPU only the all-gather half, (W-1)/W of the tensor outbound, crosses NVLink here; the
+// reduce-scatter half crossed it tile by tile while the MMAs ran.  Entry / exit ordering as in the two-shot kernel.
+// stage: this rank's [W][rows][ld / 8] array of 16-byte vectors; data.p[r]: rank r's [rows][ld / 8] output.
+template <int W, int kThreads>
+__global__ void __launch_bounds__(kThreads)
+    gather_staged_allreduce_bf16_kernel(const uint4* __restrict__ stage, const PeerPtrs data, const PeerPtrs signals,
+                                        const int rank, const uint32_t rows, const uint32_t vectors_per_row,
+                                        const uint32_t epoch, const uint32_t counter_target, int* status,
+                                        const unsigned long long timeout_ns) {
+    static_assert(W >= 2 && W <= kMaxPeers, "one NVSwitch box");
+    PeerSignals* my_signals = static_cast<PeerSignals*>(signals.p[rank]);
+    if (epoch != 0 && !enter_collective<W>(signals, my_signals, rank, epoch, status, timeout_ns)) {
+        leave_collective<W>(signals, my_signals, rank, epoch, counter_target, status, timeout_ns, false);
+        return;
+    }
+    constexpr uint32_t kRowsPerBlock = 128;  // the GEMM's BLOCK_M: ownership goes by m-blocks
+    const uint32_t num_m_blocks = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
+    const uint32_t owned_blocks = (num_m_blocks > static_cast<uint32_t>(rank)) ? (num_m_blocks - rank + W - 1) / W : 0;
+    const size_t total = static_cast<size_t>(owned_blocks) * kRowsPerBlock * vectors_per_row;
+    const size_t copy_stride = static_cast<size_t>(rows) * vectors_per_row;  // one source rank's [rows][ld] copy
+    constexpr int kVectors = (kThreads <= 512) ? 16 : 8;
+    constexpr int kUnroll = (kVectors / W) > 0 ? (kVectors / W) : 1;
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i0 = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total; i0 += stride * kUnroll) {
+        uint4 v[kUnroll][W];
+        size_t at[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const size_t i = i0 + u * stride;
+            at[u] = static_cast<size_t>(-1);
+            if (i < total) {
+                const size_t owned_row = i / vectors_per_row, col = i - owned_row * vectors_per_row;
+                const size_t row = ((owned_row / kRowsPerBlock) * W + rank) * kRowsPerBlock + owned_row % kRowsPerBlock;
+                if (row < rows) {
+                    at[u] = row * vectors_per_row + col;
+#pragma unroll
+                    for (int r = 0; r < W; ++r) v[u][r] = comm_detail::ld_sys_v4(stage + r * copy_stride + at[u]);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            if (at[u] != static_cast<size_t>(-1)) {
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int r = 0; r < W; ++r) comm_detail::accumulate(acc, v[u][r]);
+                uint4 o;
+                __nv_bfloat162 t;
+                t = __floats2bfloat162_rn(acc[0], acc[1]); o.x = *reinterpret_cast<uint32_t*>(&t);
+                t = __floats2bfloat162_rn(acc[2], acc[3]); o.y = *reinterpret_cast<uint32_t*>(&t);
+                t = __floats2bfloat162_rn(acc[4], acc[5]); o.z = *reinterpret_cast<uint32_t*>(&t);
+                t = __floats2bfloat162_rn(acc[6], acc[7]); o.w = *reinterpret_cast<uint32_t*>(&t);
+#pragma unroll
+                for (int r = 0; r < W; ++r) {
+                    const int peer = (rank + r) % W;
+                    static_cast<uint4*>(data.p[peer])[at[u]] = o;
+                }
+            }
+        }
+    }
+    if (epoch != 0) leave_collective<W>(signals, my_signals, rank, epoch, counter_target, status, timeout_ns);
+}
+
 struct AllreduceArgs {
     PeerPtrs data{};     // the same-shaped bf16 buffer on every rank; entry [rank] is local, the others peer-mapped
     void* multicast = nullptr;  // in-switch form only: the multicast address of the buffers (data is then unused)
@@ -255,7 +327,37 @@ struct AllreduceArgs {
     bool exclusive = false;                 // true: 1024-thread CTAs, one per SM: the grid occupies exactly num_ctas SMs
     int* status = nullptr;
     unsigned long long timeout_ns = 2000000000ull;
+    // gather_staged form only: this rank's staging array and the matrix shape (rows, row pitch in bf16 elements)
+    const void* stage = nullptr;
+    uint32_t rows = 0, ld = 0;
 };
+
+inline int launch_gather_staged_allreduce_bf16(const AllreduceArgs& a, cudaStream_t stream) {
+    if (a.world < 2 || a.world > kMaxPeers || a.rank < 0 || a.rank >= a.world || a.num_ctas <= 0) return kBadArgument;
+    if (a.stage == nullptr || reinterpret_cast<uintptr_t>(a.stage) % 16 != 0 || a.rows == 0 || a.ld == 0 || a.ld % 8 != 0 ||
+        a.epoch == 0)
+        return kBadArgument;
+    for (int r = 0; r < a.world; ++r) {
+        if (a.data.p[r] == nullptr || reinterpret_cast<uintptr_t>(a.data.p[r]) % 16 != 0) return kBadArgument;
+        if (a.signals.p[r] == nullptr || reinterpret_cast<uintptr_t>(a.signals.p[r]) % 4 != 0) return kBadArgument;
+    }
+    const dim3 grid(static_cast<unsigned>(a.num_ctas));
+    const uint4* stage = static_cast<const uint4*>(a.stage);
+#define YAN_LAUNCH_GATHER(W)                                                                                          \
+    gather_staged_allreduce_bf16_kernel<W, kAllreduceThreads><<<grid, kAllreduceThreads, 0, stream>>>(                \
+        stage, a.data, a.signals, a.rank, a.rows, a.ld / 8, a.epoch, a.counter_target, a.status, a.timeout_ns)
+    switch (a.world) {
+        case 2: YAN_LAUNCH_GATHER(2); break;
+        case 3: YAN_LAUNCH_GATHER(3); break;
+        case 4: YAN_LAUNCH_GATHER(4); break;
+        case 5: YAN_LAUNCH_GATHER(5); break;
+        case 6: YAN_LAUNCH_GATHER(6); break;
+        case 7: YAN_LAUNCH_GATHER(7); break;
+        default: YAN_LAUNCH_GATHER(8); break;
+    }
+#undef YAN_LAUNCH_GATHER
+    return cudaGetLastError() == cudaSuccess ? kOk : kCommFailed;
+}
 
 inline int launch_two_shot_allreduce_bf16(const AllreduceArgs& a, cudaStream_t stream) {
     if (a.world < 2 || a.world > kMaxPeers || a.rank < 0 || a.rank >= a.world || a.num_ctas <= 0) return kBadArgument;

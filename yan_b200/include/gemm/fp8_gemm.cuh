@@ -53,6 +53,11 @@ struct GemmParams {
     // and writes its fp32 partial tile to slot (b % tail_slices) * tail_tiles + b / tail_slices of `out`.
     uint32_t tile_limit = 0;
     uint32_t tail_first_tile = 0, tail_tiles = 0, tail_slices = 0;
+    // Scatter instance (kScatter, K-split over several GPUs): the tile of m-block mb is not stored to `out` but to the
+    // staging buffer of the rank that owns it, rank mb % scatter_world, at [scatter_rank][row][col] of that rank's
+    // [world][rows][ldd] array; scatter_base[r] is rank r's array as mapped into this process (entry [scatter_rank] is local).
+    void* scatter_base[8] = {};
+    uint32_t scatter_world = 0, scatter_rank = 0, scatter_rows = 0;
     int* status;  // optional device word: 0 = fine, otherwise (kDeviceTimeout << 8) | site
     unsigned long long timeout_ns;
     // optional: CTA 0 writes {clock64, globaltimer} when it starts and when it ends (4 values), so that the host can
@@ -203,6 +208,9 @@ struct GemmSmemLayout {
 #ifndef YAN_PROMO_SPLIT_HALVES
 #define YAN_PROMO_SPLIT_HALVES 0
 #endif
+#ifndef YAN_TAIL_MIN_K_BLOCKS
+#define YAN_TAIL_MIN_K_BLOCKS 96
+#endif
 #ifndef YAN_PROMO_EARLY_PROBE
 #define YAN_PROMO_EARLY_PROBE 0
 #endif
@@ -229,7 +237,11 @@ struct GemmSmemLayout {
 // instance (and the k-range, tile choice and output slot are compile-time branches) because the code of the hot loop
 // is sensitive to everything else the kernel holds: an earlier form that taught the one kernel to cut tiles lost a
 // fifth of the whole-tile schedule's speed.
-template <uint32_t BLOCK_N, uint32_t kNumStages, GemmType kGemmType, typename out_t, bool kTail = false>
+// kScatter: the instance of the row-parallel (K-split) GEMM whose epilogue is the reduce-scatter half of the
+// allreduce: every finished bf16 tile goes straight to the rank that will sum it (plain stores to peer-mapped memory,
+// 64 contiguous bytes per row piece), while the MMAs of the next tiles run; see comm/scatter_allreduce.cuh for the other
+// half.  This is the per-tile hand-over of the reference's epilogue (comm/gemm_allreduce.cu:339-410) without NVSHMEM.
+template <uint32_t BLOCK_N, uint32_t kNumStages, GemmType kGemmType, typename out_t, bool kTail = false, bool kScatter = false>
 __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     fp8_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tensor_map_a,
                     const __grid_constant__ CUtensorMap tensor_map_b) {
@@ -283,6 +295,7 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     const uint32_t num_k_blocks = p.shape_k / kBlockK;
     const uint32_t num_sb_rows = ceil_div(p.shape_n, 128u);
     static_assert(!kTail || (kGemmType == GemmType::Normal && sizeof(out_t) == 4), "the tail instance writes fp32 partials");
+    static_assert(!kScatter || (kGemmType == GemmType::Normal && sizeof(out_t) == 2 && !kTail), "the scatter instance writes bf16 tiles");
     // k-blocks [kb_begin, kb_begin + kb_count) of every tile this CTA computes: all of them, or the CTA's slice
     const uint32_t tail_slice = kTail ? blockIdx.x % p.tail_slices : 0u, tail_tile = kTail ? blockIdx.x / p.tail_slices : 0u;
     const uint32_t kb_begin = kTail ? (tail_slice * num_k_blocks) / p.tail_slices : 0u;
@@ -300,6 +313,9 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
         }
     };
 
+    // A whole-tile launch that is followed by a tail launch lets that one be scheduled at once: its CTAs take the SMs as
+    // this kernel's CTAs leave them (they read operands and write scratch only, nothing this kernel produces).
+    if (!kTail && p.tile_limit != 0) ptx::grid_dependency_launch_dependents();
     if (warp_idx == 0 && lane_idx == 0) {
         ptx::tma_prefetch_desc(&tensor_map_a);
         ptx::tma_prefetch_desc(&tensor_map_b);
@@ -593,6 +609,9 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
                     const uint32_t out_ld = kTail ? BLOCK_N : p.ldd, out_cols = kTail ? BLOCK_N : p.shape_n;
                     const uint32_t n_store = kTail ? col0 : n_first;
                     out_t* out_base = reinterpret_cast<out_t*>(p.out);
+                    if constexpr (kScatter)
+                        out_base = reinterpret_cast<out_t*>(p.scatter_base[m_block_idx % p.scatter_world]) +
+                                   static_cast<size_t>(p.scatter_rank) * p.scatter_rows * p.ldd;
 #pragma unroll
                     for (uint32_t pass = 0; pass < kColsPerWG / kStoreCols; ++pass) {
                         __syncwarp();  // the read-back of the previous pass is over
@@ -644,6 +663,12 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     }
 
     // Every role has left its loop (normally or through the bounded-wait path): free tensor memory.
+    if constexpr (kTail) {
+        // launched programmatically behind the whole-tile kernel: do not complete before that kernel has (the kernel
+        // that sums the partials waits for this one only), and let that kernel be scheduled now
+        ptx::grid_dependency_launch_dependents();
+        ptx::grid_dependency_wait();
+    }
     ptx::tcgen05_fence_before_thread_sync();
     __syncthreads();
     if (warp_idx == 2) {
@@ -680,6 +705,10 @@ struct GemmArgs {
     // along K; its contents are rewritten by every launch that uses it, nothing needs to be cleared
     void* tail_workspace = nullptr;
     size_t tail_workspace_bytes = 0;
+    // K-split with the reduce-scatter in the epilogue: staging arrays of all ranks (see GemmParams::scatter_base);
+    // scatter_world = 0: ordinary output
+    void* scatter_base[8] = {};
+    uint32_t scatter_world = 0, scatter_rank = 0;
 };
 
 // Bytes of scratch a grid of `num_sms` CTAs can use for the tail of a launch of BLOCK_N-wide tiles.
@@ -694,7 +723,7 @@ constexpr size_t tail_workspace_bytes(uint32_t num_sms, uint32_t block_n) {
 // (measured on B200: M=4096 N=7168 K=18432 533 -> 505 us; M=8192 N=3584 K=8192 230 -> 232 us).
 inline uint32_t choose_tail_slices(uint32_t tiles, uint32_t grid, uint32_t num_k_blocks) {
     const uint32_t rest = tiles % grid;
-    if (grid < 2 || tiles < grid || rest == 0 || 2 * rest > grid || num_k_blocks < 96) return 0;
+    if (grid < 2 || tiles < grid || rest == 0 || 2 * rest > grid || num_k_blocks < YAN_TAIL_MIN_K_BLOCKS) return 0;
     const uint32_t waves = tiles / grid + 1;
     if (static_cast<double>(grid - rest) / (static_cast<double>(waves) * grid) < 0.05) return 0;
     uint32_t slices = grid / rest;
@@ -709,6 +738,7 @@ __global__ void __launch_bounds__(256) reduce_tail_partials_kernel(const float* 
                                                                     uint32_t shape_m, uint32_t shape_n, uint32_t first_tile,
                                                                     uint32_t tail_tiles, uint32_t slices) {
     constexpr uint32_t kChunksPerRow = BLOCK_N / 8;
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // the partial tiles are complete (no-op for an ordinary launch)
     const uint32_t t = blockIdx.x;
     const uint32_t idx = blockIdx.y * 256 + threadIdx.x;
     const uint32_t row = idx / kChunksPerRow, chunk = idx % kChunksPerRow;
@@ -807,6 +837,27 @@ struct GemmLauncher {
             const uint32_t tiles = ceil_div(a.m, kBlockM) * ceil_div(a.n, BLOCK_N);
             grid = tiles < grid ? tiles : grid;
         }
+        if constexpr (kGemmType == GemmType::Normal && sizeof(out_t) == 2 && L::kStoreBytes != 0) {
+            if (a.scatter_world != 0) {
+                if (a.scatter_world < 2 || a.scatter_world > 8 || a.scatter_rank >= a.scatter_world) return kBadArgument;
+                for (uint32_t r = 0; r < a.scatter_world; ++r) {
+                    if (a.scatter_base[r] == nullptr || !is_aligned(a.scatter_base[r], 16)) return kBadArgument;
+                    p.scatter_base[r] = a.scatter_base[r];
+                }
+                p.scatter_world = a.scatter_world;
+                p.scatter_rank = a.scatter_rank;
+                p.scatter_rows = a.m;
+                auto scatter_kernel = fp8_gemm_kernel<BLOCK_N, kNumStages, GemmType::Normal, out_t, false, true>;
+                if (cudaFuncSetAttribute(scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemSize) != cudaSuccess) {
+                    cudaGetLastError();
+                    return kSmemTooLarge;
+                }
+                scatter_kernel<<<grid, get_num_threads_per_sm<>(BLOCK_N), kSmemSize, stream>>>(p, map_a, map_b);
+                return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+            }
+        } else {
+            if (a.scatter_world != 0) return kBadArgument;
+        }
         // A nearly empty last wave: whole tiles for the full waves, then the rest cut along K, then the sum of the cuts.
         if constexpr (kGemmType == GemmType::Normal && sizeof(out_t) == 2 && L::kStoreBytes != 0) {
             const uint32_t tiles = ceil_div(a.m, kBlockM) * ceil_div(a.n, BLOCK_N);
@@ -828,12 +879,34 @@ struct GemmLauncher {
                 tail.tail_tiles = rest;
                 tail.tail_slices = slices;
                 tail.clock_probe = nullptr;
-                tail_kernel<<<rest * slices, get_num_threads_per_sm<>(BLOCK_N), kSmemSize, stream>>>(tail, map_a, map_b);
-                const dim3 reduce_grid(rest, kBlockM * (BLOCK_N / 8) / 256);
-                reduce_tail_partials_kernel<BLOCK_N><<<reduce_grid, 256, 0, stream>>>(
-                    static_cast<const float*>(a.tail_workspace), static_cast<__nv_bfloat16*>(a.out), a.ldd, a.m, a.n,
-                    tiles - rest, rest, slices);
-                return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+                // both follow-up kernels are launched with programmatic stream serialization: the launch latencies
+                // hide behind the kernel before; ordering is kept by the waits inside them
+                cudaLaunchAttribute attr[1];
+                attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+                attr[0].val.programmaticStreamSerializationAllowed = 1;
+                cudaLaunchConfig_t cfg = {};
+                cfg.gridDim = dim3(rest * slices);
+                cfg.blockDim = dim3(get_num_threads_per_sm<>(BLOCK_N));
+                cfg.dynamicSmemBytes = kSmemSize;
+                cfg.stream = stream;
+                cfg.attrs = attr;
+                cfg.numAttrs = 1;
+                if (cudaLaunchKernelEx(&cfg, tail_kernel, tail, map_a, map_b) != cudaSuccess) {
+                    cudaGetLastError();
+                    return kLaunchFailed;
+                }
+                cfg.gridDim = dim3(rest, kBlockM * (BLOCK_N / 8) / 256);
+                cfg.blockDim = dim3(256);
+                cfg.dynamicSmemBytes = 0;
+                const float* partials = static_cast<const float*>(a.tail_workspace);
+                __nv_bfloat16* out_bf16 = static_cast<__nv_bfloat16*>(a.out);
+                const uint32_t first_tile = tiles - rest;
+                if (cudaLaunchKernelEx(&cfg, reduce_tail_partials_kernel<BLOCK_N>, partials, out_bf16, a.ldd, a.m, a.n,
+                                       first_tile, rest, slices) != cudaSuccess) {
+                    cudaGetLastError();
+                    return kLaunchFailed;
+                }
+                return kOk;
             }
         }
         kernel<<<grid, get_num_threads_per_sm<>(BLOCK_N), kSmemSize, stream>>>(p, map_a, map_b);
