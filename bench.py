@@ -38,10 +38,10 @@ M, N, K = 8192, 28672, 8192
 WORKLOAD = "C4 column-parallel prefill GEMM M=8192 N=28672 K=8192 (B sharded along N, A replicated)"
 METRIC = "FP8 GEMM TFLOP/s (% FP8 peak); small-M HBM GB/s; 1/2/4/8-GPU scaling"
 CPU_SLAB_ROWS = 256
-# DRAM bytes / algorithmic bytes of the GEMM kernel: ncu measured 211.0 MB of dram__bytes_read+write against
+# DRAM bytes / algorithmic bytes of the GEMM kernel: ncu measured 218.1 MB of dram__bytes_read+write against
 # 193.4 MB of algorithmic bytes on M=4096 N=14336 K=4096 (a case small enough to capture); L2 holds the re-used
 # operand panels at the benchmark's size too, so the same ratio is applied to its algorithmic bytes.
-GEMM_DRAM_TRAFFIC_RATIO = 1.09
+GEMM_DRAM_TRAFFIC_RATIO = 1.13
 
 
 def workload_config(world: int) -> dict:
