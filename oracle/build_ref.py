@@ -17,7 +17,9 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref", "ref_gemm_sm100")
-REFERENCE_ROOT = os.environ.get("YAN_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: YAN_REFERENCE_ROOT, or a directory named `reference` beside this repository
+REFERENCE_ROOT = os.environ.get("YAN_REFERENCE_ROOT",
+                                os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 
 
 def _cutlass_root():

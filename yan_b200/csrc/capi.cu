@@ -87,10 +87,10 @@ inline void set_rc(int* rc, int v) {
 }
 
 // Picks BLOCK_N by a wave model: cost = waves * (time of one tile relative to a 256-wide one).  The relative tile
-// times are measured (time / waves on M = 8192, K = 8192 with N = 3584 and 28672): the promotion of a k-block has a large fixed
-// part, so a narrower tile is far from proportionally cheaper, and the widths whose half does not divide 128 pay for a
-// second B scale and a 16-column tail chunk.  Large problems therefore get 256; narrower tiles win when they fill the
-// machine better (few tiles, or a last wave of 256-wide tiles that is nearly empty).
+// times are measured (time per wave on M = 8192, N = 26880, K = 4096, a shape every width divides): the promotion of a
+// k-block has a large fixed part, so a narrower tile is far from proportionally cheaper, and the widths without
+// shared-memory room for the staged epilogue (224, 192, 160, 96) or with a second B scale and a 16-column tail chunk
+// pay for that.  Large problems therefore get 256; narrower tiles win when they fill the machine better.
 int choose_block_n(int m, int n, int k, int num_sms, bool can_cut_tail) {
     static const struct { int bn; double tile_cost; } candidates[8] = {
         {256, 1.000}, {224, 1.02}, {192, 0.83}, {160, 0.79}, {128, 0.63}, {96, 0.62}, {64, 0.50}, {32, 0.47}};
