@@ -142,7 +142,8 @@ def gemm_fp8_fp8_bf16_nt(lhs: Tuple[torch.Tensor, torch.Tensor], rhs: Tuple[torc
             raise _lib.YanB200Error('gemm_fp8_fp8_bf16_nt[jit]', rc, 'see ReturnCode in include/gemm/utils.cuh')
         _jit_runtimes_used[runtime.path] = runtime
         return
-    if block_n == 0 and m > 64 and tail_cut_enabled():
+    # the cut only ever applies to long K and more tiles than CTAs (choose_tail_slices in include/gemm/fp8_gemm.cuh)
+    if block_n == 0 and k >= 96 * 128 and ceil_div(m, 128) * ceil_div(n, 256) > num_sms and tail_cut_enabled():
         # the library may cut the tiles of a nearly empty last wave along K (scratch per device and stream)
         ws = _tail_workspace(out.device, num_sms)
         _lib.call("yan_b200_gemm_fp8_fp8_bf16_nt_tail", lhs_q.data_ptr(), lhs_scales.data_ptr(), rhs_q.data_ptr(),
