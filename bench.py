@@ -21,6 +21,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -500,6 +501,9 @@ def multi_gpu_parity(rank: int, world: int, dist) -> dict:
                 entry["pass"] = entry["pass"] and bool(v)
         out[name] = entry
 
+    # forms that ADD in bf16 (NCCL's bf16 ring, the switch's bf16 reduction) round after each of the world-1 additions
+    # on top of the world rounded partials, so their distance from the oracle grows with the number of ranks
+    tol_bf16_sum = 3e-3 * math.sqrt(world)
     lhs_dev = (lhs[0].contiguous().cuda(), lhs[1].t().contiguous().cuda().t())
     # N-split: every rank writes its own column slice of a zeroed full buffer; summing the buffers assembles D
     full = torch.zeros(m, n, dtype=torch.bfloat16, device="cuda")
@@ -514,7 +518,7 @@ def multi_gpu_parity(rank: int, world: int, dist) -> dict:
     res = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
     ga.gemm_k_split_allreduce(lhs_k, rhs_k, res, partial_dtype=torch.bfloat16, num_chunks=2)
     torch.cuda.synchronize()
-    record("k_split_nccl_bf16_partials", res, d_split, 2e-3)
+    record("k_split_nccl_bf16_partials", res, d_split, tol_bf16_sum)
     ga.gemm_k_split_allreduce(lhs_k, rhs_k, res, partial_dtype=torch.float32, num_chunks=2)
     torch.cuda.synchronize()
     record("k_split_nccl_fp32_partials", res, d_ref, 1e-3)
@@ -530,7 +534,7 @@ def multi_gpu_parity(rank: int, world: int, dist) -> dict:
     rank_order_sum = acc.to(torch.bfloat16)
     try:
         from yan_b200.comm import TwoShotAllreduce
-        for name, in_switch, tol in (("two_shot", False, 2e-3), ("in_switch", True, 6e-3)):
+        for name, in_switch, tol in (("two_shot", False, 2e-3), ("in_switch", True, tol_bf16_sum)):
             try:
                 comm = TwoShotAllreduce(m, n, in_switch=in_switch)
             except Exception as e:
