@@ -71,13 +71,6 @@ namespace detail {
 // role already gave up; the caller then leaves its loop.
 __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                              const GemmParams& p, int site) {
-#if defined(YAN_WAIT_TEST_SPINS) && YAN_WAIT_TEST_SPINS > 0
-    if ((YAN_WAIT_TEST_SITES >> site) & 1) {
-#pragma unroll 1
-        for (int i = 0; i < YAN_WAIT_TEST_SPINS; ++i)
-            if (ptx::mbar_test_wait(bar, parity)) return true;
-    }
-#endif
     if (ptx::mbar_try_wait(bar, parity)) return true;
     // Fast path first: when the phase is already complete (the usual case for the role that bounds the kernel) the
     // timer is never read.
