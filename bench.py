@@ -39,10 +39,12 @@ M, N, K = 8192, 28672, 8192
 WORKLOAD = "C4 column-parallel prefill GEMM M=8192 N=28672 K=8192 (B sharded along N, A replicated)"
 METRIC = "FP8 GEMM TFLOP/s (% FP8 peak); small-M HBM GB/s; 1/2/4/8-GPU scaling"
 CPU_SLAB_ROWS = 256
-# DRAM bytes / algorithmic bytes of the GEMM kernel: ncu measured 218.1 MB of dram__bytes_read+write against
-# 193.4 MB of algorithmic bytes on M=4096 N=14336 K=4096 (a case small enough to capture); L2 holds the re-used
-# operand panels at the benchmark's size too, so the same ratio is applied to its algorithmic bytes.
-GEMM_DRAM_TRAFFIC_RATIO = 1.13
+# DRAM bytes of one GEMM launch of the benchmark's own 1-GPU workload (M=8192 N=28672 K=8192), from an ncu capture
+# of three launches inside the quantize + GEMM sequence with the caches left as the sequence leaves them:
+# dram__bytes_read 1023.5 MB + dram__bytes_write 482.6 MB.  The reads are A once (67 MB) plus B (235 MB, larger than
+# the L2) once per band of 16 tile rows, four times in all; the writes are D (470 MB).  No capture exists for the
+# narrower shards of the multi-GPU runs, so their line carries null.
+GEMM_DRAM_TRAFFIC_BYTES_1GPU = 1023.5e6 + 482.6e6
 
 
 def workload_config(world: int) -> dict:
@@ -752,9 +754,11 @@ def run_ours(args) -> None:
     achieved = gemm_flops / (gemm_ms / 1e3) / 1e12
     fp8_peak = 2.0 * peaks["bf16_tflops"]
     algo_bytes = M * K + 4 * M * (K // 128) + n_local * K + 4 * (n_local // 128) * (K // 128) + 2 * M * n_local
-    traffic = GEMM_DRAM_TRAFFIC_RATIO * algo_bytes
+    traffic = GEMM_DRAM_TRAFFIC_BYTES_1GPU if world == 1 else None
     roofline = {"kernel": "fp8_gemm_kernel<BLOCK_N=256>", "bound": "tensor", "achieved": achieved, "peak": fp8_peak,
                 "unit": "TFLOP/s", "frac": achieved / fp8_peak, "traffic": traffic, "algorithmic_bytes_per_launch": algo_bytes,
+                "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of this workload's launch, caches as the "
+                                  "step leaves them" if world == 1 else "no capture of this shard",
                 "peak_source": f"2 x {peaks['source']} bf16 burst {peaks['bf16_tflops']} TFLOP/s "
                                "(e4m3 tensor rate is twice bf16; no FP8 figure is measured on this pool)",
                 "frac_of_2x_sustained_bf16": achieved / (2.0 * peaks["bf16_tflops_sustained"]),

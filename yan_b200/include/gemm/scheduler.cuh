@@ -16,7 +16,11 @@ enum class GemmType {
     GroupedMasked       // A is [G,M_max,K], B is [G,N,K]; grouped_layout[g] = valid rows of group g
 };
 
-template <GemmType kGemmType, uint32_t BLOCK_M, uint32_t BLOCK_N, uint32_t kNum1DBlocksPerGroup = 16>
+#ifndef YAN_SCHED_BAND
+#define YAN_SCHED_BAND 16
+#endif
+
+template <GemmType kGemmType, uint32_t BLOCK_M, uint32_t BLOCK_N, uint32_t kNum1DBlocksPerGroup = YAN_SCHED_BAND>
 struct Scheduler {
     int current_iter = -1;
     uint32_t num_m_blocks;  // Normal / Contiguous: over shape_m; Masked: per group maximum
