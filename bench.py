@@ -385,10 +385,17 @@ def bench_reference_blackwell_gemm(peaks, m: int = 8192, n: int = 8192, k: int =
 
 
 def _time_k_split(step, dist, steps: int, m: int, n: int, k: int, flops: bool = True) -> dict:
+    import yan_b200
     for _ in range(3):
         step()
     dist.barrier()
     torch.cuda.synchronize()
+    # a wait between ranks that ran out during the warm-up (on any rank): the form is not timed -- every further launch
+    # would sit out its bound as well
+    expired = torch.tensor([float(yan_b200.read_device_status(reset=True) != 0)], device="cuda", dtype=torch.float64)
+    dist.all_reduce(expired, op=dist.ReduceOp.MAX)
+    if expired.item() != 0:
+        return {"not_timed": "a bounded wait between the ranks ran out during the warm-up"}
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
@@ -403,7 +410,7 @@ def _time_k_split(step, dist, steps: int, m: int, n: int, k: int, flops: bool = 
     return {"ms_per_step": t.item(), "TFLOP/s": 2.0 * m * n * k / (t.item() / 1e3) / 1e12}
 
 
-def bench_k_split(rank: int, world: int, dist, steps: int = 10) -> dict:
+def bench_k_split(rank: int, world: int, dist, steps: int = 10, parity: dict = None) -> dict:
     """Row-parallel GEMM + allreduce (M=4096, N=8192, K=28672 split along K over the ranks): per step each rank
     quantizes its K shard of A, computes a full-size bf16 partial D in row chunks and sums the partials with an NCCL
     allreduce that overlaps the next chunk's GEMM.  Time = max over ranks, device events."""
@@ -421,6 +428,12 @@ def bench_k_split(rank: int, world: int, dist, steps: int = 10) -> dict:
     out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
     comm_stream = torch.cuda.Stream()
     results = {}
+
+    def checked(prefix: str) -> bool:
+        """False when the parity pass before the timed legs saw this form fail: it is then neither run nor timed."""
+        if not parity:
+            return True
+        return all(v.get("pass", True) for key, v in parity.items() if key.startswith(prefix) and isinstance(v, dict))
     for label, chunks in (("NCCL, single allreduce", 1), ("NCCL, 4 row chunks overlapped", 4)):
         def step():
             yan_b200.per_token_cast_to_fp8(a, out=lhs)
@@ -430,6 +443,8 @@ def bench_k_split(rank: int, world: int, dist, steps: int = 10) -> dict:
     # straight into the shared buffer), and the two collectives alone on the same 64 MiB tensor.
     try:
         from yan_b200.comm import TwoShotAllreduce
+        if not checked("k_split_two_shot") or not checked("two_shot_reduce_rows"):
+            raise RuntimeError("the two-shot kernel failed the parity pass")
         comm = TwoShotAllreduce(m, n)
         variants = (("", 1, 24), (", 2 row chunks overlapped (24 SMs to the collective)", 2, 24),
                     (", 2 row chunks overlapped (64 SMs to the collective)", 2, 64),
@@ -440,6 +455,8 @@ def bench_k_split(rank: int, world: int, dist, steps: int = 10) -> dict:
                 ga.gemm_k_split_two_shot(lhs, rhs, comm, num_chunks=chunks, comm_sms=comm_sms, comm_stream=comm_stream)
             results["two-shot peer allreduce" + suffix] = _time_k_split(step, dist, steps, m, n, k)
         try:
+            if not checked("k_split_in_switch") or not checked("in_switch_reduce_rows"):
+                raise RuntimeError("the in-switch kernel failed the parity pass")
             comm_sw = TwoShotAllreduce(m, n, in_switch=True)
             for suffix, chunks, comm_sms in variants:
                 def step():
@@ -452,6 +469,8 @@ def bench_k_split(rank: int, world: int, dist, steps: int = 10) -> dict:
             results["in-switch peer allreduce"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
         try:
             from yan_b200.comm import TileFusedAllreduce
+            if not checked("k_split_tile_fused"):
+                raise RuntimeError("the tile-fused form failed the parity pass")
             fused = TileFusedAllreduce(m, n)
 
             def step():
@@ -663,6 +682,11 @@ def run_ours(args) -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    if world > 1:
+        # the ranks of this benchmark are lined up by barriers before every collective leg, so a wait between ranks that
+        # takes seconds is a fault, not drift: 3 s instead of the library's 10 s keeps a faulty form from eating the run
+        from yan_b200 import _lib as _yan_lib
+        _yan_lib.lib().yan_b200_set_collective_timeout_ns(3_000_000_000)
     parity = multi_gpu_parity(rank, world, dist) if world > 1 else None
 
     for _ in range(args.warmup):
@@ -793,7 +817,7 @@ def run_ours(args) -> None:
     torch.cuda.empty_cache()
 
     if world > 1 and not args.no_extras:
-        k_split = bench_k_split(rank, world, dist)
+        k_split = bench_k_split(rank, world, dist, parity=parity)
         if rank == 0:
             line["other_workloads"] = [k_split]
     if rank == 0 and world == 1 and not args.no_extras:
