@@ -477,6 +477,16 @@ def bench_k_split(rank: int, world: int, dist, steps: int = 10, parity: dict = N
                 yan_b200.per_token_cast_to_fp8(a, out=lhs)
                 fused.gemm_and_reduce(lhs, rhs)
             results["tile-fused: reduce-scatter in the GEMM epilogue + all-gather kernel"] = _time_k_split(step, dist, steps, m, n, k)
+            # its two halves alone (the scatter writes peers' staging arrays that nobody reads meanwhile; the gather sums
+            # whatever the last scatter left there)
+            results["tile-fused, first half alone: GEMM with the scatter epilogue"] = _time_k_split(
+                lambda: fused.scatter_gemm(lhs, rhs), dist, steps, m, n, k, flops=False)
+            results["tile-fused, second half alone: gather kernel"] = _time_k_split(
+                lambda: fused.gather(), dist, steps, m, n, k, flops=False)
+
+            def plain_gemm():
+                yan_b200.gemm_fp8_fp8_bf16_nt(lhs, rhs, out)
+            results["this rank's K-shard GEMM alone, local output"] = _time_k_split(plain_gemm, dist, steps, m, n, k, flops=False)
             fused.close()
         except Exception as e:
             results["tile-fused"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}

@@ -252,6 +252,12 @@ class TileFusedAllreduce:
         self._clock = CollectiveClock()
 
     def gemm_and_reduce(self, lhs_shard, rhs_shard, block_n: int = 0) -> torch.Tensor:
+        """Both halves on the current stream; returns `buffer` (valid once the stream has run the second kernel)."""
+        self.scatter_gemm(lhs_shard, rhs_shard, block_n)
+        return self.gather()
+
+    def scatter_gemm(self, lhs_shard, rhs_shard, block_n: int = 0) -> None:
+        """First half: this rank's K shard of the GEMM, every finished tile stored into its owner's staging array."""
         from ..jit_kernels.utils import get_col_major_tensor, get_num_sms
         lhs_q, lhs_scales = lhs_shard
         rhs_q, rhs_scales = rhs_shard
@@ -266,6 +272,11 @@ class TileFusedAllreduce:
         _lib.call("yan_b200_gemm_fp8_fp8_bf16_nt_scatter", lhs_q.data_ptr(), lhs_scales.data_ptr(), rhs_q.data_ptr(),
                   rhs_scales.data_ptr(), self._stage, self.world, self.rank, m, self.n, k, self.n, stream, get_num_sms(),
                   block_n)
+
+    def gather(self) -> torch.Tensor:
+        """Second half: waits (on the device, bounded) until every rank's scatter has landed, sums the staged copies of
+        the rows this rank owns and stores the sums into every rank's `buffer`."""
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
         epoch, counter_target = self._clock.next_launch(self.num_ctas)
         _lib.call("yan_b200_allreduce_bf16_gather_staged", ctypes.c_void_p(self.stage.data_ptr()), self._data, self._signals,
                   self.world, self.rank, self.m, self.n, epoch, counter_target, self.num_ctas, stream)
