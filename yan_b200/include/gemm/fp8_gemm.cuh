@@ -159,7 +159,7 @@ struct E4m3Out {
     uint8_t code;
 };
 
-template <uint32_t BLOCK_N, uint32_t kNumStages>
+template <uint32_t BLOCK_N, uint32_t kNumStages, bool kWideBoxes = false>
 struct GemmSmemLayout {
     static constexpr uint32_t kNumTmemBufs = (BLOCK_N > 128) ? 2 : 4;
     static constexpr uint32_t kTmemColsUsed = kNumTmemBufs * BLOCK_N;
@@ -172,7 +172,10 @@ struct GemmSmemLayout {
     // Output staging: every promotion warp owns one 32-row x 64-byte box (2 KB).  A lane writes 64 bytes of its own
     // output row into the box, the warp reads the box back eight rows at a time and stores 64 contiguous bytes per
     // row piece, so that one store instruction covers 8 x 64 bytes instead of 32 x 16 bytes of 32 different lines.
-    static constexpr uint32_t kStoreBoxBytes = 2048;
+    // kWideBoxes (the scatter instance, whose pieces cross NVLink): 32 rows x 128 bytes per box, so that a store
+    // instruction covers 4 x 128 bytes -- whole 128-byte lines on the link instead of half lines.
+    static constexpr uint32_t kStoreRowBytes = kWideBoxes ? 128 : 64;
+    static constexpr uint32_t kStoreBoxBytes = 32 * kStoreRowBytes;
     static constexpr uint32_t kNumStoreBoxes = 8;
     static constexpr uint32_t kOffStore = kOffB + kNumStages * SMEM_B_SIZE_PER_STAGE;
     static constexpr uint32_t kStoreBytes =
@@ -246,7 +249,7 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     fp8_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tensor_map_a,
                     const __grid_constant__ CUtensorMap tensor_map_b) {
 #if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ >= 1000)
-    using L = GemmSmemLayout<BLOCK_N, kNumStages>;
+    using L = GemmSmemLayout<BLOCK_N, kNumStages, kScatter && GemmSmemLayout<BLOCK_N, kNumStages, true>::kStoreBytes != 0>;
     using Sched = Scheduler<kGemmType, kBlockM, BLOCK_N>;
     constexpr uint32_t kNumTmemBufs = L::kNumTmemBufs;
     constexpr uint32_t kNumMathWGs = get_num_math_warpgroups(BLOCK_N);
@@ -274,8 +277,8 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     constexpr uint32_t kScaleDepth = YAN_PROMO_SCALE_DEPTH;
     // bf16 / fp32 output through the staging boxes (see GemmSmemLayout) when a warpgroup's columns are whole 64-byte pieces.
     constexpr bool kStagedStore = L::kStoreBytes != 0 && sizeof(out_t) >= 2 && kNumMathWarps == L::kNumStoreBoxes &&
-                                  (kColsPerWG * sizeof(out_t)) % 64 == 0;
-    constexpr uint32_t kStoreCols = 64 / (sizeof(out_t) >= 2 ? sizeof(out_t) : 2);  // columns per 64-byte box row
+                                  (kColsPerWG * sizeof(out_t)) % L::kStoreRowBytes == 0;
+    constexpr uint32_t kStoreCols = L::kStoreRowBytes / (sizeof(out_t) >= 2 ? sizeof(out_t) : 2);  // columns per box row
     // Half-width MMA streams: each warpgroup's columns are produced and recycled on their own barriers.
     constexpr bool kSplitHalves = (YAN_PROMO_SPLIT_HALVES != 0);
     constexpr uint32_t kNumHalves = kSplitHalves ? 2 : 1;
@@ -597,10 +600,16 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
             }
             if constexpr (kStagedStore) {
                 if (alive) {
-                    // Lane r fills row r (64 bytes) of the warp's box; 16-byte chunk j of a row sits at chunk
-                    // j ^ ((r / 2) % 4), which keeps both the row-wise writes and the read-back free of bank conflicts.
+                    // Lane r fills row r (64 bytes; 128 in the wide boxes) of the warp's box; 16-byte chunk j of a row sits
+                    // at chunk j ^ ((r / 2) % 4) (j ^ (r % 8) in the wide boxes), which keeps both the row-wise writes and
+                    // the read-back free of bank conflicts.
+                    constexpr uint32_t kRowBytes = L::kStoreRowBytes, kChunksPerRow = kRowBytes / 16;
+                    constexpr uint32_t kRowsPerStore = 32 / kChunksPerRow;  // box rows one store instruction covers
+                    auto swizzled = [](uint32_t chunk, uint32_t r) {
+                        return kChunksPerRow == 4 ? (chunk ^ ((r >> 1) & 3u)) : (chunk ^ (r & 7u));
+                    };
                     const uint32_t box = ptx::smem_u32(smem + L::kOffStore + (warp_idx - 4) * L::kStoreBoxBytes);
-                    const uint32_t row_addr = box + lane_idx * 64u;
+                    const uint32_t row_addr = box + lane_idx * kRowBytes;
                     constexpr uint32_t kElemsPerChunk = 16 / sizeof(out_t);
                     // the tail instance writes whole partial tiles into its slot of the scratch: [slot][128][BLOCK_N]
                     const uint32_t tile_row0 =
@@ -616,7 +625,7 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
                     for (uint32_t pass = 0; pass < kColsPerWG / kStoreCols; ++pass) {
                         __syncwarp();  // the read-back of the previous pass is over
 #pragma unroll
-                        for (uint32_t j = 0; j < 4; ++j) {
+                        for (uint32_t j = 0; j < kChunksPerRow; ++j) {
                             const float* a = acc + pass * kStoreCols + j * kElemsPerChunk;
                             uint4 v;
                             if constexpr (sizeof(out_t) == 2) {
@@ -630,15 +639,17 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
                                 v = make_uint4(__float_as_uint(a[0]), __float_as_uint(a[1]), __float_as_uint(a[2]),
                                                __float_as_uint(a[3]));
                             }
-                            ptx::st_shared_v4(row_addr + ((j ^ ((lane_idx >> 1) & 3u)) << 4), v);
+                            ptx::st_shared_v4(row_addr + (swizzled(j, lane_idx) << 4), v);
                         }
                         __syncwarp();
                         // read back: instruction i covers box rows 8i .. 8i+7, lane l -> row 8i + l/4, chunk l%4
-                        const uint32_t n_chunk = n_store + pass * kStoreCols + (lane_idx & 3u) * kElemsPerChunk;
+                        // (wide boxes: rows 4i .. 4i+3, lane l -> row 4i + l/8, chunk l%8)
+                        const uint32_t my_chunk = lane_idx % kChunksPerRow;
+                        const uint32_t n_chunk = n_store + pass * kStoreCols + my_chunk * kElemsPerChunk;
 #pragma unroll
-                        for (uint32_t i = 0; i < 4; ++i) {
-                            const uint32_t r = i * 8u + (lane_idx >> 2);
-                            const uint4 v = ptx::ld_shared_v4(box + r * 64u + (((lane_idx & 3u) ^ ((r >> 1) & 3u)) << 4));
+                        for (uint32_t i = 0; i < 32 / kRowsPerStore; ++i) {
+                            const uint32_t r = i * kRowsPerStore + lane_idx / kChunksPerRow;
+                            const uint4 v = ptx::ld_shared_v4(box + r * kRowBytes + (swizzled(my_chunk, r) << 4));
                             const uint32_t out_row = tile_row0 + r;
                             if (out_row < row_limit && n_chunk < out_cols)
                                 *reinterpret_cast<uint4*>(out_base + static_cast<size_t>(out_row) * out_ld + n_chunk) = v;
@@ -839,6 +850,8 @@ struct GemmLauncher {
         }
         if constexpr (kGemmType == GemmType::Normal && sizeof(out_t) == 2 && L::kStoreBytes != 0) {
             if (a.scatter_world != 0) {
+                // only the widths whose epilogue goes through the staging boxes know the owners' staging arrays
+                if (BLOCK_N != 256 && BLOCK_N != 128) return kBadArgument;
                 if (a.scatter_world < 2 || a.scatter_world > 8 || a.scatter_rank >= a.scatter_world) return kBadArgument;
                 for (uint32_t r = 0; r < a.scatter_world; ++r) {
                     if (a.scatter_base[r] == nullptr || !is_aligned(a.scatter_base[r], 16)) return kBadArgument;
@@ -848,11 +861,15 @@ struct GemmLauncher {
                 p.scatter_rank = a.scatter_rank;
                 p.scatter_rows = a.m;
                 auto scatter_kernel = fp8_gemm_kernel<BLOCK_N, kNumStages, GemmType::Normal, out_t, false, true>;
-                if (cudaFuncSetAttribute(scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemSize) != cudaSuccess) {
+                // the scatter instance stages its output in wider boxes where they fit (same rule as in the kernel)
+                using Wide = GemmSmemLayout<BLOCK_N, kNumStages, true>;
+                constexpr uint32_t kScatterSmem = Wide::kStoreBytes != 0 ? Wide::kSmemSize : kSmemSize;
+                if (static_cast<int>(kScatterSmem) > max_smem) return kSmemTooLarge;
+                if (cudaFuncSetAttribute(scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScatterSmem) != cudaSuccess) {
                     cudaGetLastError();
                     return kSmemTooLarge;
                 }
-                scatter_kernel<<<grid, get_num_threads_per_sm<>(BLOCK_N), kSmemSize, stream>>>(p, map_a, map_b);
+                scatter_kernel<<<grid, get_num_threads_per_sm<>(BLOCK_N), kScatterSmem, stream>>>(p, map_a, map_b);
                 return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
             }
         } else {
