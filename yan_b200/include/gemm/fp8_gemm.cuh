@@ -242,8 +242,8 @@ struct GemmSmemLayout {
 // fifth of the whole-tile schedule's speed.
 // kScatter: the instance of the row-parallel (K-split) GEMM whose epilogue is the reduce-scatter half of the
 // allreduce: every finished bf16 tile goes straight to the rank that will sum it (plain stores to peer-mapped memory,
-// 64 contiguous bytes per row piece), while the MMAs of the next tiles run; see comm/scatter_allreduce.cuh for the other
-// half.  This is the per-tile hand-over of the reference's epilogue (comm/gemm_allreduce.cu:339-410) without NVSHMEM.
+// 128 contiguous bytes per row piece), while the MMAs of the next tiles run; gather_staged_allreduce_bf16_kernel in
+// comm/peer_allreduce.cuh is the other half.  This is the per-tile hand-over of the reference's epilogue (comm/gemm_allreduce.cu:339-410) without NVSHMEM.
 template <uint32_t BLOCK_N, uint32_t kNumStages, GemmType kGemmType, typename out_t, bool kTail = false, bool kScatter = false>
 __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     fp8_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tensor_map_a,
