@@ -201,6 +201,9 @@ struct GemmSmemLayout {
 //                          warpgroup has read it.  0: one full-width stream, one barrier pair per buffer.
 //   YAN_PROMO_EARLY_PROBE  1: the next k-block's TMEM-full barrier is probed (without blocking) right after this
 //                          k-block's last load, so that the answer arrives under the last FMAs.
+//   YAN_WIDE_STORE_BOXES   1: every instance stages its output in 32 x 128-byte boxes (the scatter instance always does);
+//                          for a local output it measured within +-1 % on the large shapes and 3 % slower on
+//                          M=8192 N=3584 K=8192, so the default keeps the 64-byte rows and the 16 KB of shared memory.
 // Measured and dropped: handing the TMEM read port back and forth between the two warps of a sub-partition through
 // mbarriers (an arrive-to-wait hand-over costs ~100 cycles: 778 and 1163 cycles per k-block for 64- and 32-column turns
 // against 343 without), and four promotion warpgroups (874 cycles per k-block against 733: the per-k-block bookkeeping
@@ -216,6 +219,9 @@ struct GemmSmemLayout {
 #endif
 #ifndef YAN_PROMO_EARLY_PROBE
 #define YAN_PROMO_EARLY_PROBE 0
+#endif
+#ifndef YAN_WIDE_STORE_BOXES
+#define YAN_WIDE_STORE_BOXES 0
 #endif
 
 // -DYAN_PHASE_STAMPS: CTA 0 also accumulates, per role, the cycles it spends waiting and working and writes them
@@ -249,7 +255,7 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     fp8_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tensor_map_a,
                     const __grid_constant__ CUtensorMap tensor_map_b) {
 #if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ >= 1000)
-    using L = GemmSmemLayout<BLOCK_N, kNumStages, kScatter && GemmSmemLayout<BLOCK_N, kNumStages, true>::kStoreBytes != 0>;
+    using L = GemmSmemLayout<BLOCK_N, kNumStages, (kScatter || YAN_WIDE_STORE_BOXES != 0) && GemmSmemLayout<BLOCK_N, kNumStages, true>::kStoreBytes != 0>;
     using Sched = Scheduler<kGemmType, kBlockM, BLOCK_N>;
     constexpr uint32_t kNumTmemBufs = L::kNumTmemBufs;
     constexpr uint32_t kNumMathWGs = get_num_math_warpgroups(BLOCK_N);
@@ -781,7 +787,7 @@ inline bool is_aligned(const void* p, size_t a) { return (reinterpret_cast<uintp
 
 template <uint32_t BLOCK_N, uint32_t kNumStages, GemmType kGemmType, typename out_t>
 struct GemmLauncher {
-    using L = GemmSmemLayout<BLOCK_N, kNumStages>;
+    using L = GemmSmemLayout<BLOCK_N, kNumStages, YAN_WIDE_STORE_BOXES != 0 && GemmSmemLayout<BLOCK_N, kNumStages, true>::kStoreBytes != 0>;
     static constexpr uint32_t kSmemSize = L::kSmemSize;
 
     static int launch(const GemmArgs& a, cudaStream_t stream) {
