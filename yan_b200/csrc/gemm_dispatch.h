@@ -20,8 +20,11 @@ int launch_gemm_bn256(GemmType type, OutKind out, const GemmArgs& args, cudaStre
 
 // Default pipeline depth per BLOCK_N: 128-wide k-block stages (16 KB of A + BLOCK_N * 128 bytes of B each) that fit
 // in 227 KB next to the barriers, at most 8.
+#ifndef YAN_STAGES_256
+#define YAN_STAGES_256 4
+#endif
 constexpr uint32_t default_num_stages(uint32_t block_n) {
-    return block_n == 256 ? 4 : block_n >= 192 ? 5 : block_n == 160 ? 6 : block_n == 128 ? 6 : 8;
+    return block_n == 256 ? YAN_STAGES_256 : block_n >= 192 ? 5 : block_n == 160 ? 6 : block_n == 128 ? 6 : 8;
 }
 
 }  // namespace yan
