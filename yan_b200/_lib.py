@@ -97,3 +97,13 @@ def call_rc(name: str, *args) -> int:
     rc = ctypes.c_int(0)
     getattr(lib(), name)(*args, ctypes.byref(rc))
     return rc.value
+
+
+def current_stream_ptr() -> ctypes.c_void_p:
+    """The current CUDA stream of the current device as a raw handle.  Uses torch's direct binding where it exists:
+    building a torch.cuda.Stream object per call costs several microseconds, which shows on small launches."""
+    import torch
+    raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    if raw is not None:
+        return ctypes.c_void_p(raw(torch.cuda.current_device()))
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)

@@ -192,7 +192,7 @@ class TwoShotAllreduce:
         row_end = self.m if row_end is None else row_end
         assert 0 <= row_begin < row_end <= self.m
         ctas = num_ctas or self.num_ctas
-        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        stream = _lib.current_stream_ptr()
         begin, count = row_begin * self.n, (row_end - row_begin) * self.n
         if self.in_switch:
             name, target = "yan_b200_allreduce_bf16_in_switch", ctypes.c_void_p(self._arena.multicast_ptr)
@@ -268,7 +268,7 @@ class TileFusedAllreduce:
         lhs_scales = get_col_major_tensor(lhs_scales)
         if lhs_scales.stride(1) != m:
             lhs_scales = lhs_scales.t().contiguous().t()
-        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        stream = _lib.current_stream_ptr()
         _lib.call("yan_b200_gemm_fp8_fp8_bf16_nt_scatter", lhs_q.data_ptr(), lhs_scales.data_ptr(), rhs_q.data_ptr(),
                   rhs_scales.data_ptr(), self._stage, self.world, self.rank, m, self.n, k, self.n, stream, get_num_sms(),
                   block_n)
@@ -276,7 +276,7 @@ class TileFusedAllreduce:
     def gather(self) -> torch.Tensor:
         """Second half: waits (on the device, bounded) until every rank's scatter has landed, sums the staged copies of
         the rows this rank owns and stores the sums into every rank's `buffer`."""
-        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        stream = _lib.current_stream_ptr()
         epoch, counter_target = self._clock.next_launch(self.num_ctas)
         _lib.call("yan_b200_allreduce_bf16_gather_staged", ctypes.c_void_p(self.stage.data_ptr()), self._data, self._signals,
                   self.world, self.rank, self.m, self.n, epoch, counter_target, self.num_ctas, stream)

@@ -83,7 +83,7 @@ def get_best_configs(m: int, n: int, k: int, num_sms: int) -> Tuple[int, int, in
 
 
 def _stream_ptr() -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    return _lib.current_stream_ptr()
 
 
 def _check_operands(lhs, lhs_scales, rhs, rhs_scales, out, out_dtype) -> Tuple[int, int, int]:
@@ -121,7 +121,7 @@ def gemm_fp8_fp8_bf16_nt(lhs: Tuple[torch.Tensor, torch.Tensor], rhs: Tuple[torc
     if m == 1 or lhs_scales.stride(1) != m:
         lhs_scales = lhs_scales.t().contiguous().t()
     num_sms = get_num_sms()
-    if int(os.environ.get("YAN_FP8_GEMM_JIT", "0")):
+    if os.environ.get("YAN_FP8_GEMM_JIT", "0") not in ("0", ""):
         from .tuner import jit_tuner
         assert out.stride(0) == n, "the JIT specialisation writes a dense [M, N] output"
         # smem_size = 0: each candidate checks its own requirement against the device limit and reports

@@ -16,7 +16,7 @@ from .. import _lib
 
 
 def _stream_ptr() -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    return _lib.current_stream_ptr()
 
 
 def per_token_cast_to_fp8(x: torch.Tensor, out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None

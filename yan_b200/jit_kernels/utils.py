@@ -35,6 +35,8 @@ def get_col_major_tensor(x: torch.Tensor) -> torch.Tensor:
     """Column-major version of a 2D (or batched 3D) tensor, shape unchanged: stride (1, rows).
     Returns `x` itself when it already has that layout (yan/jit_kernels/utils.py:58-85)."""
     assert x.dim() in (2, 3)
+    if x.dim() == 2 and x.stride(0) == 1 and x.stride(1) == x.shape[0]:
+        return x  # the usual case on the hot path: nothing to build
     remove_dim = False
     if x.dim() == 2:
         x, remove_dim = x.unsqueeze(0), True
