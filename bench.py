@@ -832,18 +832,28 @@ def run_ours(args) -> None:
             line["other_workloads"] = [k_split]
     if rank == 0 and world == 1 and not args.no_extras:
         extras = []
+
+        def leg(fn, *fn_args, **fn_kwargs):
+            # every side measurement is a short burst; half a second of idle in front of it keeps the power-cap state the
+            # previous leg left (a GPU that has just run tens of milliseconds of dense GEMMs clocks lower for a while)
+            # out of its figure
+            torch.cuda.synchronize()
+            time.sleep(0.5)
+            extras.append(fn(*fn_args, **fn_kwargs))
         for m_small in (16, 64):
-            extras.append(bench_decode(m_small, peaks))
-        extras.append(bench_dense("C3 mid-size projection", 4096, 7168, 18432, peaks))
-        extras.append(bench_dense("C1 CPU-runnable", 256, 1024, 1024, peaks))
-        extras.append(bench_fused_epilogue(4096, 7168, 18432, peaks=peaks))
-        extras.append(bench_fused_epilogue(8192, 7168, 2048, peaks=peaks))
-        extras.append(bench_fused_epilogue(M, N, K, iters=5, peaks=peaks))
-        extras.append(bench_grouped(peaks))
-        extras.append(bench_reference_blackwell_gemm(peaks))
+            leg(bench_decode, m_small, peaks)
+        leg(bench_dense, "C3 mid-size projection", 4096, 7168, 18432, peaks)
+        leg(bench_dense, "C1 CPU-runnable", 256, 1024, 1024, peaks)
+        leg(bench_fused_epilogue, 4096, 7168, 18432, peaks=peaks)
+        leg(bench_fused_epilogue, 8192, 7168, 2048, peaks=peaks)
+        leg(bench_fused_epilogue, M, N, K, iters=5, peaks=peaks)
+        leg(bench_grouped, peaks)
+        leg(bench_reference_blackwell_gemm, peaks)
         if sustained is not None:
             extras.append(sustained)
         line["other_workloads"] = extras
+        line["other_workloads_note"] = ("each side measurement is a burst of about ten launches started after 0.5 s of idle; "
+                                        "the sustained figure of the main workload is the entry timed over ~2 s")
         from yan_b200.utils import perf_log
         for record in extras:  # one JSON line per side measurement when YAN_PERF_LOG names a file
             perf_log(record)

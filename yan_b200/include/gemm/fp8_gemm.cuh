@@ -277,10 +277,14 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
     // multiple of 16 columns: two B scales per k-block, chosen per group of 16 columns (the case the reference
     // handles for BLOCK_N not dividing BLOCK_K, fp8_gemm.cuh:55-61,149-160).
     constexpr bool kTwoScales = (128 % kColsPerWG != 0) && (kColsPerWG % 128 != 0);
+    // k-blocks between the load of a scale and its use (the promotion loop is unrolled by this number).  0 = by tile
+    // width: 2 for the wide tiles, whose k-block lasts about as long as an L2 round trip, 4 for the narrow ones.
+    // Measured on 256-wide tiles (C4, same box): 4 -> 1736 us, 3 -> 1737 us, 2 -> 1654 us, 1 -> 1680 us on a second box
+    // where 2 gave 1692 us; the shorter loop body is what helps.
 #ifndef YAN_PROMO_SCALE_DEPTH
-#define YAN_PROMO_SCALE_DEPTH 4
+#define YAN_PROMO_SCALE_DEPTH 0
 #endif
-    constexpr uint32_t kScaleDepth = YAN_PROMO_SCALE_DEPTH;
+    constexpr uint32_t kScaleDepth = YAN_PROMO_SCALE_DEPTH != 0 ? YAN_PROMO_SCALE_DEPTH : (BLOCK_N >= 128 ? 2 : 4);
     // bf16 / fp32 output through the staging boxes (see GemmSmemLayout) when a warpgroup's columns are whole 64-byte pieces.
     constexpr bool kStagedStore = L::kStoreBytes != 0 && sizeof(out_t) >= 2 && kNumMathWarps == L::kNumStoreBoxes &&
                                   (kColsPerWG * sizeof(out_t)) % L::kStoreRowBytes == 0;
