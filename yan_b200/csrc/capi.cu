@@ -93,7 +93,7 @@ inline void set_rc(int* rc, int v) {
 // pay for that.  Large problems therefore get 256; narrower tiles win when they fill the machine better.
 int choose_block_n(int m, int n, int k, int num_sms, bool can_cut_tail) {
     static const struct { int bn; double tile_cost; } candidates[8] = {
-        {256, 1.000}, {224, 1.02}, {192, 0.83}, {160, 0.79}, {128, 0.63}, {96, 0.62}, {64, 0.50}, {32, 0.47}};
+        {256, 1.000}, {224, 1.08}, {192, 0.84}, {160, 0.82}, {128, 0.67}, {96, 0.72}, {64, 0.57}, {32, 0.50}};
     int best = 256;
     double best_cost = -1.0;
     for (const auto& c : candidates) {

@@ -65,7 +65,7 @@ def get_smem_size(block_n: int, num_stages: int) -> int:
 
 
 # time of one tile relative to a 256-wide one (measured; see choose_block_n in csrc/capi.cu)
-_TILE_COST = {256: 1.000, 224: 1.02, 192: 0.83, 160: 0.79, 128: 0.63, 96: 0.62, 64: 0.50, 32: 0.47}
+_TILE_COST = {256: 1.000, 224: 1.08, 192: 0.84, 160: 0.82, 128: 0.67, 96: 0.72, 64: 0.57, 32: 0.50}
 
 
 def get_best_configs(m: int, n: int, k: int, num_sms: int) -> Tuple[int, int, int]:
