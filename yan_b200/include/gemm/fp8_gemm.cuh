@@ -285,6 +285,13 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
 #define YAN_PROMO_SCALE_DEPTH 0
 #endif
     constexpr uint32_t kScaleDepth = YAN_PROMO_SCALE_DEPTH != 0 ? YAN_PROMO_SCALE_DEPTH : (BLOCK_N >= 128 ? 2 : 4);
+    // The wide tiles run a single copy of the loop body and shift the ring instead (C4: 1654 -> 1616 us on one box;
+    // with three slots the same form measured 1672 us); YAN_PROMO_SHIFT_RING = 0 / 1 forces either form.
+#ifndef YAN_PROMO_SHIFT_RING
+#define YAN_PROMO_SHIFT_RING (-1)
+#endif
+    constexpr bool kShiftRing = YAN_PROMO_SHIFT_RING >= 0 ? (YAN_PROMO_SHIFT_RING != 0) : (kScaleDepth == 2);
+    constexpr uint32_t kLoopUnroll = kShiftRing ? 1 : kScaleDepth;
     // bf16 / fp32 output through the staging boxes (see GemmSmemLayout) when a warpgroup's columns are whole 64-byte pieces.
     constexpr bool kStagedStore = L::kStoreBytes != 0 && sizeof(out_t) >= 2 && kNumMathWarps == L::kNumStoreBoxes &&
                                   (kColsPerWG * sizeof(out_t)) % L::kStoreRowBytes == 0;
@@ -516,19 +523,30 @@ __global__ void __launch_bounds__(get_num_threads_per_sm<>(BLOCK_N), 1)
 #pragma unroll
             for (uint32_t j = 0; j < kColsPerWG; ++j) acc[j] = 0.0f;
 
-            for (uint32_t kb0 = 0; kb0 < kb_count && alive; kb0 += kScaleDepth) {
-#pragma unroll
-                for (uint32_t i = 0; i < kScaleDepth; ++i) {
+            // kShiftRing: one copy of the loop body, the ring of scales moved down one slot per k-block (a few register
+            // moves); otherwise the body is unrolled once per ring slot and every copy uses its own slot.
+            for (uint32_t kb0 = 0; kb0 < kb_count && alive; kb0 += kLoopUnroll) {
+#pragma unroll(kLoopUnroll)
+                for (uint32_t i = 0; i < kLoopUnroll; ++i) {
                     const uint32_t kb = kb0 + i;
-                    if (!alive || kb >= kb_count) continue;
-                    const float scale = sa_ring[i] * sb_ring[i];
+                    if (!alive || (kLoopUnroll > 1 && kb >= kb_count)) continue;
+                    const uint32_t use = kShiftRing ? 0 : i, fill = kShiftRing ? kScaleDepth - 1 : i;
+                    const float scale = sa_ring[use] * sb_ring[use];
                     float scale_hi = scale;
-                    if constexpr (kTwoScales) scale_hi = sa_ring[i] * sb_hi_ring[i];
+                    if constexpr (kTwoScales) scale_hi = sa_ring[use] * sb_hi_ring[use];
+                    if constexpr (kShiftRing) {
+#pragma unroll
+                        for (uint32_t r = 0; r + 1 < kScaleDepth; ++r) {
+                            sa_ring[r] = sa_ring[r + 1];
+                            sb_ring[r] = sb_ring[r + 1];
+                            if constexpr (kTwoScales) sb_hi_ring[r] = sb_hi_ring[r + 1];
+                        }
+                    }
                     if (kb + kScaleDepth < kb_count) {
-                        sa_ring[i] = row_ok ? __ldg(sa_next) : 0.0f;
+                        sa_ring[fill] = row_ok ? __ldg(sa_next) : 0.0f;
                         sa_next += p.sa_ld;
-                        sb_ring[i] = __ldg(sb_ptr + kb + kScaleDepth);
-                        if constexpr (kTwoScales) sb_hi_ring[i] = __ldg(sb_hi_ptr + kb + kScaleDepth);
+                        sb_ring[fill] = __ldg(sb_ptr + kb + kScaleDepth);
+                        if constexpr (kTwoScales) sb_hi_ring[fill] = __ldg(sb_hi_ptr + kb + kScaleDepth);
                     }
                     YAN_STAMP(w0);
                     const bool ok = (kEarlyProbe && next_ready) ||
